@@ -15,6 +15,7 @@ from .registry import (
 from . import llama as _llama  # registers LlamaForCausalLM
 from . import sinorax as _sinorax  # registers Sinorax
 from . import zeladra as _zeladra  # registers Zeladra
+from . import tanupel as _tanupel  # registers Tanupel
 
 __all__ = [
     "ConfigError",

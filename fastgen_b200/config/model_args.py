@@ -54,6 +54,8 @@ class LayerSpec:
     ffn: Optional[PartSpec]  # None: a layer without a feed-forward (and without its norm)
     ffn_norm: Optional[PartSpec]
     extra: Tuple[Tuple[str, str, PartSpec], ...] = ()
+    #: the arrangement's own constants (its parameter dataclass), for arrangements that have some
+    block_params: Any = None
 
 
 @dataclass(frozen=True)
@@ -62,11 +64,14 @@ class ScheduleEntry:
 
     ``layer`` indexes ``ModelArgs.layers``.  ``kv_from`` names an earlier
     schedule entry whose cache this run reads without writing one of its own;
-    ``None`` gives the run a cache of its own.
+    ``None`` gives the run a cache of its own.  ``step_row``: before this run, row ``step_row``
+    of the model's table of step vectors (``ModelArgs.step_table_name``) is added to every token's
+    residual stream (a run of layers that is passed several times marks each pass that way).
     """
 
     layer: int
     kv_from: Optional[int] = None
+    step_row: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -94,9 +99,20 @@ class ModelArgs:
     #: so many residual streams side by side ([T, streams, dim], all equal to the embedding at the
     #: start, summed before the final norm); ``None``: the one ordinary stream [T, dim]
     streams: Optional[int] = None
+    #: tensor [rows, dim] of vectors that schedule entries add to the residual stream
+    #: (``ScheduleEntry.step_row``); ``None``: the model has none
+    step_table_name: Optional[str] = None
+    step_table_rows: int = 0
 
     def __post_init__(self) -> None:
         n = len(self.layers)
+        for pos, entry in enumerate(self.schedule):
+            if entry.step_row is not None:
+                if self.step_table_name is None or not 0 <= entry.step_row < self.step_table_rows:
+                    raise ConfigError(f"schedule entry {pos} adds row {entry.step_row} of a table of "
+                                      f"{self.step_table_rows} step vectors")
+                if self.streams is not None:
+                    raise ConfigError("step vectors are added to one residual stream, not to several")
         for pos, entry in enumerate(self.schedule):
             if not 0 <= entry.layer < n:
                 raise ConfigError(

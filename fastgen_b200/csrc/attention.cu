@@ -23,7 +23,7 @@ extern "C" int fg_attention_simt(const void* q, int q_stride, void* out, int out
                                  int table_width, int page_size, int n_pages, const int* pos,
                                  const int* tile_req, const int* tile_tok0, const int* tile_ntok,
                                  int n_tiles, int n_heads, int n_kv_heads, int head_dim, int window,
-                                 int keep_first, float scale, int* status, cudaStream_t stream) {
+                                 int keep_first, float scale, float softcap, int* status, cudaStream_t stream) {
   using namespace fg_attn;
   if (n_tiles == 0) return 0;
   FG_CHECK_ARG(head_dim == FG_HEAD_DIM, "fg_attention_simt: library built for head size %d, got %d",
@@ -43,7 +43,7 @@ extern "C" int fg_attention_simt(const void* q, int q_stride, void* out, int out
     kern<<<grid, THREADS, smem, stream>>>((const float*)q, q_stride, (float*)out, out_stride,
                                           (const float*)k_pages, (const float*)v_pages, block_table,
                                           table_width, page_size, n_pages, pos, tile_req, tile_tok0,
-                                          tile_ntok, n_kv_heads, group, hpb, window, keep_first, scale, status);
+                                          tile_ntok, n_kv_heads, group, hpb, window, keep_first, scale, status, softcap);
   } else if (dtype == FG_BF16) {
     auto kern = attention_simt_kernel<__nv_bfloat16, FG_HEAD_DIM>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -52,7 +52,7 @@ extern "C" int fg_attention_simt(const void* q, int q_stride, void* out, int out
         (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride,
         (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table, table_width,
         page_size, n_pages, pos, tile_req, tile_tok0, tile_ntok, n_kv_heads, group, hpb, window, keep_first,
-        scale, status);
+        scale, status, softcap);
   } else {
     FG_CHECK_ARG(false, "fg_attention_simt: bad dtype %d", dtype);
   }
@@ -199,7 +199,8 @@ extern "C" int fg_attention_prefill_bf16(const void* q, int q_stride, void* out,
                                          int table_width, int page_size, int n_pages, const int* pos,
                                          const int* tile_req, const int* tile_tok0, const int* tile_ntok,
                                          int n_tiles, int n_heads, int n_kv_heads, int head_dim, int window,
-                                         int keep_first, float scale, int* status, cudaStream_t stream) {
+                                         int keep_first, float scale, float softcap, int* status,
+                                         cudaStream_t stream) {
   using namespace fg_mma;
   if (n_tiles == 0) return 0;
   FG_CHECK_ARG(head_dim == FG_HEAD_DIM, "fg_attention_prefill_bf16: library built for head size %d, got %d",
@@ -223,7 +224,8 @@ extern "C" int fg_attention_prefill_bf16(const void* q, int q_stride, void* out,
       (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pages,
       (const __nv_bfloat16*)v_pages, block_table, table_width, page_size, n_pages, pos, tile_req, tile_tok0,
       tile_ntok, n_kv_heads, group, hpb, window, scale * 1.4426950408889634f, status, nullptr, nullptr, nullptr,
-      window > 0 ? keep_first : 0);
+      window > 0 ? keep_first : 0, softcap > 0.f ? softcap * 1.4426950408889634f : 0.f,
+      softcap > 0.f ? scale / softcap : 0.f);
   FG_CHECK_LAUNCH("fg_attention_prefill_bf16");
   return 0;
 }
@@ -260,7 +262,7 @@ extern "C" int fg_attention_sigmoid_prefill_bf16(const void* q, int q_stride, vo
   kern<<<grid, THREADS, smem, stream>>>(
       (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pages,
       (const __nv_bfloat16*)v_pages, block_table, table_width, page_size, n_pages, pos, tile_req, tile_tok0,
-      tile_ntok, n_kv_heads, group, hpb, window, scale, status, gate, r1, r2, 0);
+      tile_ntok, n_kv_heads, group, hpb, window, scale, status, gate, r1, r2, 0, 0.f, 0.f);
   FG_CHECK_LAUNCH("fg_attention_sigmoid_prefill_bf16");
   return 0;
 }
@@ -273,7 +275,7 @@ extern "C" int fg_attention_decode_bf16(const void* q, int q_stride, void* out, 
                                         const int* seq_req, const int* seq_tok, int n_seqs, int n_heads,
                                         int n_kv_heads, int head_dim, int window, int keep_first, float scale,
                                         float* scratch, long long scratch_floats, int max_splits,
-                                        const float* out_freqs, int* status, cudaStream_t stream) {
+                                        const float* out_freqs, float softcap, int* status, cudaStream_t stream) {
   using namespace fg_mma;
   if (n_seqs == 0) return 0;
   FG_CHECK_ARG(head_dim == FG_HEAD_DIM, "fg_attention_decode_bf16: library built for head size %d, got %d",
@@ -302,7 +304,9 @@ extern "C" int fg_attention_decode_bf16(const void* q, int q_stride, void* out, 
   kern<<<grid, THREADS, smem, stream>>>((const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pages,
                                         (const __nv_bfloat16*)v_pages, block_table, table_width, page_size,
                                         n_pages, pos, seq_req, seq_tok, n_heads, n_kv_heads, group, window,
-                                        scale_log2, scratch, max_splits, status, keep_first);
+                                        scale_log2, scratch, max_splits, status, keep_first,
+                                        softcap > 0.f ? softcap * 1.4426950408889634f : 0.f,
+                                        softcap > 0.f ? scale / softcap : 0.f);
   FG_CHECK_LAUNCH("fg_attention_decode_bf16");
   dim3 cgrid(n_heads, n_seqs);
   attention_combine_kernel<FG_HEAD_DIM><<<cgrid, COMBINE_THREADS, 0, stream>>>(

@@ -213,6 +213,16 @@ constexpr size_t prefill_smem_bytes() {
 // (gate, r1, r2: float32 per query head, each may be null), not normalised over the keys: no running
 // maximum, no rescaling, no division at the end; scale_log2 is then the plain scale.  The weights are
 // rounded to bfloat16 for the second product as the probabilities are.
+// A raw score on its way into the base-2 softmax: times scale * log2(e), or, with a cap on the
+// scores (cap_log2 = cap * log2(e) > 0, scale_by_cap = scale / cap), cap * tanh(score * scale / cap)
+// in the same units.  tanh(x) = 1 - 2 / (1 + e^2x) on the special-function unit: exact at both
+// ends, an absolute error of a few 1e-7 around zero.
+__device__ __forceinline__ float capped_score(float s, float scale_log2, float cap_log2, float scale_by_cap) {
+  if (cap_log2 <= 0.f) return s * scale_log2;
+  const float e2x = __expf(2.f * s * scale_by_cap);
+  return cap_log2 * (1.f - __fdividef(2.f, 1.f + e2x));
+}
+
 template <int HD, bool SIGMOID = false>
 __global__ void __launch_bounds__(THREADS)
 attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* __restrict__ out,
@@ -222,7 +232,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
                          const int* __restrict__ tile_req, const int* __restrict__ tile_tok0,
                          const int* __restrict__ tile_ntok, int n_kv_heads, int group, int heads_per_block,
                          int window, float scale_log2, int* status, const float* __restrict__ gate,
-                         const float* __restrict__ dist_r1, const float* __restrict__ dist_r2, int keep_first) {
+                         const float* __restrict__ dist_r1, const float* __restrict__ dist_r2, int keep_first,
+                         float cap_log2, float scale_by_cap) {
   // keep_first (with a window): so many of the sequence's first positions stay visible to every
   // query; the key tiles that hold them are walked before the tiles of the window
   constexpr int LD = Tile<HD>::LD;
@@ -365,7 +376,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
             }
             s[nt][e] = vis ? wgt : 0.f;
           } else {
-            s[nt][e] = vis ? s[nt][e] * scale_log2 : -INFINITY;
+            s[nt][e] = vis ? capped_score(s[nt][e], scale_log2, cap_log2, scale_by_cap) : -INFINITY;
           }
         }
       }
@@ -469,7 +480,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                         const int* __restrict__ pos, const int* __restrict__ seq_req,
                         const int* __restrict__ seq_tok, int n_heads, int n_kv_heads, int group,
                         int window, float scale_log2, float* __restrict__ scratch, int max_splits,
-                        int* status, int keep_first) {
+                        int* status, int keep_first, float cap_log2, float scale_by_cap) {
   static_assert(THREADS >= DECODE_SPLIT, "one thread per key position computes its row offset");
   constexpr int LD = Tile<HD>::LD;
   constexpr int NT = 4;  // 32 key positions per warp
@@ -531,7 +542,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
       for (int e = 0; e < 4; ++e) {
         const int j = k0 + warp * 32 + nt * 8 + 2 * (lane & 3) + (e & 1);
         const bool vis = (j >= k_begin || j < keep_first) && j < k_end;
-        s[nt][e] = vis ? s[nt][e] * scale_log2 : -INFINITY;
+        s[nt][e] = vis ? capped_score(s[nt][e], scale_log2, cap_log2, scale_by_cap) : -INFINITY;
       }
     float o[HD / 8][4];
 #pragma unroll

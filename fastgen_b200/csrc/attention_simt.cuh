@@ -33,7 +33,7 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
                       int n_pages, const int* __restrict__ pos, const int* __restrict__ tile_req,
                       const int* __restrict__ tile_tok0, const int* __restrict__ tile_ntok,
                       int n_kv_heads, int group, int heads_per_block, int window, int keep_first,
-                      float scale, int* status) {
+                      float scale, int* status, float softcap) {
   constexpr int HP = HD + 1;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float(*Qs)[HP] = reinterpret_cast<float(*)[HP]>(smem_raw);
@@ -154,7 +154,10 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
       const int r = warp + 4 * i;
       const int p = row_pos[r];
       const bool visible = has_key && p >= 0 && j <= p && (window <= 0 || j > p - window || j < keep_first);
-      const float sv = visible ? s[i] * scale : -INFINITY;
+      // with a cap, the scaled score is squashed to cap * tanh(score / cap)
+      float sc = s[i] * scale;
+      if (softcap > 0.f) sc = softcap * tanhf(sc / softcap);
+      const float sv = visible ? sc : -INFINITY;
       const float m_tile = warp_max(sv);
       const float m_new = fmaxf(m_run[i], m_tile);
       float pr = 0.f, al = 1.f;

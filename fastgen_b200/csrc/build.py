@@ -39,6 +39,7 @@ CORE_SOURCES = [
     "errors.cu",
     "embedding.cu",
     "rmsnorm.cu",
+    "rmsnorm_sum.cu",
     "dyt.cu",
     "stream_norm.cu",
     "mamba2.cu",
@@ -200,6 +201,16 @@ def attention_library(head_dim: int) -> ctypes.CDLL:
     )
 
 
+def delta_rule_library() -> ctypes.CDLL:
+    """The kernels of the gated delta rule (compiled when a model with such a mixer is bound)."""
+    return load("fg_delta", ["delta_rule.cu", "errors.cu"])
+
+
+def moe_library() -> ctypes.CDLL:
+    """The kernels of the feed-forward with routed experts."""
+    return load("fg_moe", ["moe.cu", "errors.cu"])
+
+
 def latent_library(rank: int, rot_dim: int) -> ctypes.CDLL:
     """The tensor-core kernels of the attention over a cached latent, compiled per latent size."""
     return load(f"fg_latent_r{rank}_t{rot_dim}", ["latent_mma.cu", "errors.cu"],
@@ -217,6 +228,8 @@ def build_all(head_dims: Sequence[int] = (16, 32, 64, 128), latent_sizes: Sequen
     """Compile every library (used by the build check and before shipping); the latent-attention
     library for the given (latent, rotated part) sizes."""
     _compile("fg_core", CORE_SOURCES)
+    _compile("fg_delta", ["delta_rule.cu", "errors.cu"])
+    _compile("fg_moe", ["moe.cu", "errors.cu"])
     for rank, rot in latent_sizes:
         _compile(f"fg_latent_r{rank}_t{rot}", ["latent_mma.cu", "errors.cu"],
                  [f"FG_LATENT_RANK={rank}", f"FG_LATENT_ROT={rot}"])

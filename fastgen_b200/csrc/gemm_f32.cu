@@ -11,8 +11,9 @@
 namespace {
 constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;  // 256 threads, 4x4 outputs each
 
+template <typename TA>
 __global__ void __launch_bounds__(256)
-gemm_f32_nt_kernel(const float* __restrict__ A, int lda, const float* __restrict__ W, int ldw,
+gemm_f32_nt_kernel(const TA* __restrict__ A, int lda, const float* __restrict__ W, int ldw,
                    float* __restrict__ C, int ldc, int M, int N, int K, const float* __restrict__ bias) {
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
@@ -33,7 +34,7 @@ gemm_f32_nt_kernel(const float* __restrict__ A, int lda, const float* __restrict
     for (int u = 0; u < 4; ++u) {
       const int kk = k0 + lk + u;
       const int am = m0 + lr, wn = n0 + lr;
-      As[lk + u][lr] = (am < M && kk < K) ? A[(size_t)am * lda + kk] : 0.f;
+      As[lk + u][lr] = (am < M && kk < K) ? to_f32<TA>(A[(size_t)am * lda + kk]) : 0.f;
       Ws[lk + u][lr] = (wn < N && kk < K) ? W[(size_t)wn * ldw + kk] : 0.f;
     }
     __syncthreads();
@@ -70,7 +71,25 @@ extern "C" int fg_gemm_f32_nt(const float* A, int lda, const float* W, int ldw, 
   FG_CHECK_ARG(K > 0 && lda >= K && ldw >= K && ldc >= N, "fg_gemm_f32_nt: bad sizes M=%d N=%d K=%d", M, N, K);
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   FG_CHECK_ARG(grid.y <= 65535, "fg_gemm_f32_nt: M=%d too large", M);
-  gemm_f32_nt_kernel<<<grid, 256, 0, stream>>>(A, lda, W, ldw, C, ldc, M, N, K, bias);
+  gemm_f32_nt_kernel<float><<<grid, 256, 0, stream>>>(A, lda, W, ldw, C, ldc, M, N, K, bias);
   FG_CHECK_LAUNCH("fg_gemm_f32_nt");
+  return 0;
+}
+
+// The same product with a left operand of either type (a_dtype): 16-bit activations are widened
+// as they are loaded and everything after that is float32.  For the small products that a design
+// wants in 32-bit whatever the serving type is (a router's logits).
+extern "C" int fg_gemm_f32_nt_from(const void* A, int a_dtype, int lda, const float* W, int ldw, float* C, int ldc,
+                                   int M, int N, int K, cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  FG_CHECK_ARG(K > 0 && lda >= K && ldw >= K && ldc >= N, "fg_gemm_f32_nt_from: bad sizes M=%d N=%d K=%d", M, N, K);
+  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+  FG_CHECK_ARG(grid.y <= 65535, "fg_gemm_f32_nt_from: M=%d too large", M);
+  if (a_dtype == FG_F32)
+    gemm_f32_nt_kernel<float><<<grid, 256, 0, stream>>>((const float*)A, lda, W, ldw, C, ldc, M, N, K, nullptr);
+  else
+    gemm_f32_nt_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)A, lda, W, ldw, C, ldc, M, N, K,
+                                                                nullptr);
+  FG_CHECK_LAUNCH("fg_gemm_f32_nt_from");
   return 0;
 }

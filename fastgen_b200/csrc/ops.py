@@ -58,7 +58,11 @@ _CORE_SIGNATURES = {
     "fg_dyt": [_P, _P, _I, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _P],
     "fg_bias_act": [_P, _P, _I, _I, _I, _I, _P],
     "fg_scale_softcap": [_P, _I, _I, _F, _F, _P],
-    "fg_rope_kv_write": [_P, _I, _P, _I, _P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "fg_rope_kv_write": [_P, _I, _P, _I, _P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P,
+                         _P, _P],
+    "fg_qk_rstd": [_P, _L, _I, _I, _P, _L, _I, _I, _I, _P, _F, _P, _I, _P],
+    "fg_rmsnorm_sum": [_P, _P, _P, _I, _I, _P, _P, _I, _I, _P, _I, _P, _I, _I, _F, _P],
+    "fg_gemm_f32_nt_from": [_P, _I, _I, _P, _I, _P, _I, _I, _I, _I, _P],
     "fg_gemm_f32_nt": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _P, _P],
     "fg_gemm_skinny_bf16": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P, _I, _P],
     "fg_gemm_skinny_swiglu_bf16": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _P],
@@ -71,8 +75,8 @@ _CORE_SIGNATURES = {
 }
 
 _ATTN_SIGNATURES = {
-    "fg_attention_simt": [_P, _I, _P, _I, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P,
-                          _P],
+    "fg_attention_simt": [_P, _I, _P, _I, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F,
+                          _P, _P],
     "fg_attention_sigmoid": [_P, _I, _P, _I, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F,
                              _P, _P, _P, _P, _P],
     "fg_attention_sigmoid_prefill_tc5_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I,
@@ -81,10 +85,10 @@ _ATTN_SIGNATURES = {
                                          _P, _P, _P, _P, ctypes.c_longlong, _I, _P, _P],
     "fg_attention_sigmoid_prefill_bf16": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I,
                                           _F, _P, _P, _P, _P, _P],
-    "fg_attention_prefill_bf16": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P,
-                                  _P],
+    "fg_attention_prefill_bf16": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F,
+                                  _P, _P],
     "fg_attention_decode_bf16": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P,
-                                 ctypes.c_longlong, _I, _P, _P, _P],
+                                 ctypes.c_longlong, _I, _P, _F, _P, _P],
     "fg_attention_prefill_tma_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I,
                                       _I, _F, _I, _P, _P],
     "fg_attention_prefill_tc5_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I,
@@ -173,6 +177,41 @@ def latent(rank: int, rot_dim: int):
         lib.fg_latent_mma_scratch_floats.restype = ctypes.c_longlong
         _latent[key] = lib
     return lib
+
+
+_DELTA_SIGNATURES = {
+    "fg_delta_scan": [_P, _L, _P, _L, _P, _L, _I, _P, _P, _P, _L, _P, _L, _P, _P, _I, _I, _I, _I, _I, _P],
+    "fg_head_norm_gate": [_P, _L, _P, _L, _I, _P, _P, _L, _P, _I, _I, _I, _F, _P],
+}
+_MOE_SIGNATURES = {
+    "fg_moe_route": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+    "fg_moe_plan": [_P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P],
+    "fg_moe_gemm": [_P, _L, _P, _P, _P, _L, _I, _I, _I, _P, _I, _P, _P, _P, _P, _I, _P],
+    "fg_moe_gemm_mma": [_P, _L, _P, _P, _P, _L, _I, _I, _P, _I, _P, _P, _P, _P, _I, _P],
+    "fg_moe_combine": [_P, _L, _P, _P, _P, _L, _I, _I, _I, _I, _P],
+}
+_delta = None
+_moe = None
+
+
+def delta_rule():
+    """The library of the gated delta rule."""
+    global _delta
+    if _delta is None:
+        lib = build.delta_rule_library()
+        _declare(lib, _DELTA_SIGNATURES)
+        _delta = lib
+    return _delta
+
+
+def moe():
+    """The library of the feed-forward with routed experts."""
+    global _moe
+    if _moe is None:
+        lib = build.moe_library()
+        _declare(lib, _MOE_SIGNATURES)
+        _moe = lib
+    return _moe
 
 
 def core():
@@ -551,6 +590,145 @@ class Ops:
             _ptr(rows), n, dim, float(eps), _stream()))
         return out
 
+    def rmsnorm_sum(self, h, terms, weight, eps: float, out=None, row=None, rows=None, one_plus: bool = False):
+        """``h += row + sum_i coef_i * delta_i`` (float32), then ``out = rmsnorm(h) * weight`` (times
+        ``1 + weight`` with ``one_plus``).  ``terms`` is a sequence of ``(delta [T, dim], coef)`` of one
+        dtype (at most four); ``row`` a float32 [dim] vector or ``None``.  With ``out=None`` only the sum
+        is done; with ``rows`` only those rows are summed and normed and ``h`` stays as it was."""
+        assert h.is_contiguous() and h.dtype == torch.float32
+        dim = h.shape[1]
+        n = h.shape[0] if rows is None else rows.numel()
+        terms = list(terms)
+        dtypes = {d.dtype for d, _ in terms}
+        assert len(dtypes) <= 1, "the summands of one sum have one type"
+        for d, _ in terms:
+            assert d.is_contiguous() and d.shape == h.shape
+        if row is not None:
+            assert row.dtype == torch.float32 and row.is_contiguous() and row.numel() == dim
+        if out is not None:
+            assert out.is_contiguous() and out.shape == (n, dim) and weight is not None and weight.is_contiguous()
+        assert rows is None or (rows.dtype == torch.int32 and out is not None)
+        ptrs = (c_void_p * max(1, len(terms)))(*[d.data_ptr() for d, _ in terms])
+        coefs = (c_float * max(1, len(terms)))(*[float(c) for _, c in terms])
+        _check(self.lib, self.lib.fg_rmsnorm_sum(
+            _ptr(h), ptrs, coefs, len(terms), _code(terms[0][0].dtype) if terms else 0, _ptr(row), _ptr(weight),
+            _code(weight.dtype) if weight is not None else 0, int(one_plus), _ptr(out),
+            _code(out.dtype) if out is not None else 0, _ptr(rows), n, dim, float(eps), _stream()))
+        return out
+
+    def linear_f32(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        """``x @ w.T`` in float32 whatever the serving type: ``w`` [N, K] float32, ``x`` [M, K] of either
+        type (16-bit activations are widened as they are read); IEEE sums in ascending k."""
+        m, k = x.shape
+        n = w.shape[0]
+        assert w.dtype == torch.float32 and w.shape[1] == k and x.stride(1) == 1 and w.stride(1) == 1
+        out = torch.empty((m, n), dtype=torch.float32, device=x.device)
+        _check(self.lib, self.lib.fg_gemm_f32_nt_from(_ptr(x), _code(x.dtype), x.stride(0), _ptr(w), w.stride(0),
+                                                      _ptr(out), out.stride(0), m, n, k, _stream()))
+        return out
+
+    # -- the gated delta rule ---------------------------------------------------------------------
+    def conv_silu(self, proj, offset: int, channels: int, weight, state, conv_offset: int, taps: int, ctx):
+        """Causal convolution per channel with SiLU, without a bias, over the columns
+        ``offset .. + channels`` of ``proj`` (see ``mamba2_conv``): float32 [T, channels]."""
+        return self.mamba2_conv(proj, offset, channels, weight, None, state, conv_offset, taps, ctx)
+
+    def delta_scan(self, qkv, a, b, dt_bias, a_log, state, ctx, heads: int, kv_heads: int, d: int, dv: int):
+        """The gated delta rule per (sequence, head), token by token in float32, from and into ``state``
+        [slots, .] (a slot's first ``heads * dv * d`` numbers, laid out [heads][dv][d]):
+        ``S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q`` with q, k made unit vectors
+        (q also times ``d ** -0.5``), ``g = exp(-exp(a_log) softplus(a + dt_bias))``, ``beta =
+        sigmoid(b)``.  ``qkv`` float32 [T, q | k | v] (``kv_heads * d`` twice, ``heads * dv``); ``a``
+        [T, heads * d] and ``b`` [T, heads] strided views of the compute dtype.  Returns o float32
+        [T, heads * dv]."""
+        lib = delta_rule()
+        t = qkv.shape[0]
+        assert qkv.dtype == torch.float32 and qkv.stride(1) == 1 and qkv.shape[1] == 2 * kv_heads * d + heads * dv
+        assert a.stride(1) == 1 and b.stride(1) == 1 and a.dtype == b.dtype and a.shape == (t, heads * d)
+        assert b.shape == (t, heads) and state.dtype == torch.float32 and state.is_contiguous()
+        assert dt_bias.dtype == torch.float32 and dt_bias.numel() == heads * d and dt_bias.is_contiguous()
+        assert a_log.dtype == torch.float32 and a_log.numel() == heads and a_log.is_contiguous()
+        out = torch.empty((t, heads * dv), dtype=torch.float32, device=qkv.device)
+        _check(lib, lib.fg_delta_scan(
+            _ptr(qkv), qkv.stride(0), _ptr(a), a.stride(0), _ptr(b), b.stride(0), _code(a.dtype), _ptr(dt_bias),
+            _ptr(a_log), _ptr(out), out.stride(0), _ptr(state), state.stride(0), _ptr(ctx.seq_slot),
+            _ptr(ctx.seq_start), ctx.n_seqs, heads, kv_heads, d, dv, _stream()))
+        return out
+
+    def head_norm_gate(self, o, z, weight, heads: int, dv: int, eps: float, ctx) -> torch.Tensor:
+        """Per head ``o * rsqrt(mean(o^2) + eps) * weight * sigmoid(z)``: ``o`` float32 [T, heads * dv],
+        ``z`` of the compute dtype (which the result has), ``weight`` float32 [dv] shared by the heads."""
+        lib = delta_rule()
+        t = o.shape[0]
+        assert o.dtype == torch.float32 and o.stride(1) == 1 and z.stride(1) == 1 and z.shape == o.shape
+        assert weight.dtype == torch.float32 and weight.numel() == dv and weight.is_contiguous()
+        out = torch.empty((t, heads * dv), dtype=z.dtype, device=o.device)
+        _check(lib, lib.fg_head_norm_gate(
+            _ptr(o), o.stride(0), _ptr(z), z.stride(0), _code(z.dtype), _ptr(weight), _ptr(out), out.stride(0),
+            _ptr(ctx.req), t, heads, dv, float(eps), _stream()))
+        return out
+
+    # -- routed experts -----------------------------------------------------------------------------
+    def moe_route(self, logits, correction, top: int, ctx, renormalize: bool = False):
+        """Softmax over the experts (float32), choice of the ``top`` largest ``score + correction``
+        (equal ones: the lower index), weights = the chosen experts' scores (with ``renormalize``:
+        divided by their sum).  Returns (ids int32
+        [T, top], weights float32 [T, top]); padding tokens get expert -1."""
+        lib = moe()
+        t, n = logits.shape
+        assert logits.dtype == torch.float32 and logits.is_contiguous()
+        assert correction is None or (correction.dtype == torch.float32 and correction.numel() == n)
+        ids = torch.empty((t, top), dtype=torch.int32, device=logits.device)
+        weights = torch.empty((t, top), dtype=torch.float32, device=logits.device)
+        _check(lib, lib.fg_moe_route(_ptr(logits), _ptr(correction), _ptr(ids), _ptr(weights), _ptr(ctx.req), t, n,
+                                     int(top), int(renormalize), _stream()))
+        return ids, weights
+
+    def moe_experts(self, x, ids, weights, w1, w3, w2) -> torch.Tensor:
+        """``sum_k weights[t, k] * expert_{ids[t, k]}(x[t])`` with expert ``e`` the gated feed-forward
+        ``w2[e] (silu(w1[e] x) * (w3[e] x))``; ``w1``, ``w3`` [E, F, K] and ``w2`` [E, K, F] stacked.
+        The (token, choice) pairs are sorted by expert on the device and the products run over tiles of
+        one expert's rows: on the tensor cores in bfloat16 where the sizes allow, else (and in float32)
+        with float32 sums in ascending order."""
+        lib = moe()
+        t, k = x.shape
+        n_experts, f, _ = w1.shape
+        top = ids.shape[1]
+        pairs = t * top
+        assert x.stride(1) == 1 and w1.is_contiguous() and w3.is_contiguous() and w2.is_contiguous()
+        assert w1.shape == w3.shape and w2.shape == (n_experts, k, f) and w1.dtype == x.dtype == w2.dtype
+        mma = (x.dtype == torch.bfloat16 and k % 8 == 0 and f % 8 == 0 and x.stride(0) % 8 == 0
+               and x.data_ptr() % 16 == 0 and hasattr(lib, "fg_moe_gemm_mma") and not os.environ.get("FG_NO_MOE_MMA"))
+        tile_rows = lib.fg_moe_mma_tile_rows() if mma else lib.fg_moe_gemm_tile_rows()
+        max_tiles = -(-pairs // tile_rows) + n_experts - 1
+        plan = torch.empty(2 * pairs + 3 * max_tiles + 1, dtype=torch.int32, device=x.device)
+        row_pair, pair_row = plan[:pairs], plan[pairs : 2 * pairs]
+        o = 2 * pairs
+        tile_expert, tile_row0, tile_n = plan[o : o + max_tiles], plan[o + max_tiles : o + 2 * max_tiles], \
+            plan[o + 2 * max_tiles : o + 3 * max_tiles]
+        n_tiles = plan[o + 3 * max_tiles :]
+        _check(lib, lib.fg_moe_plan(_ptr(ids), pairs, n_experts, tile_rows, _ptr(row_pair), _ptr(pair_row),
+                                    _ptr(tile_expert), _ptr(tile_row0), _ptr(tile_n), _ptr(n_tiles), max_tiles,
+                                    _stream()))
+        act = torch.empty((pairs, f), dtype=x.dtype, device=x.device)
+        y = torch.empty((pairs, k), dtype=x.dtype, device=x.device)
+        tiles = (_ptr(tile_expert), _ptr(tile_row0), _ptr(tile_n), _ptr(n_tiles), max_tiles, _stream())
+        if mma:
+            _check(lib, lib.fg_moe_gemm_mma(_ptr(x), x.stride(0), _ptr(w1), _ptr(w3), _ptr(act), act.stride(0), f, k,
+                                            _ptr(row_pair), top, *tiles))
+            _check(lib, lib.fg_moe_gemm_mma(_ptr(act), act.stride(0), _ptr(w2), None, _ptr(y), y.stride(0), k, f,
+                                            None, top, *tiles))
+        else:
+            code = _code(x.dtype)
+            _check(lib, lib.fg_moe_gemm(_ptr(x), x.stride(0), _ptr(w1), _ptr(w3), _ptr(act), act.stride(0), code, f, k,
+                                        _ptr(row_pair), top, *tiles))
+            _check(lib, lib.fg_moe_gemm(_ptr(act), act.stride(0), _ptr(w2), None, _ptr(y), y.stride(0), code, k, f,
+                                        None, top, *tiles))
+        out = torch.empty((t, k), dtype=x.dtype, device=x.device)
+        _check(lib, lib.fg_moe_combine(_ptr(y), y.stride(0), _ptr(weights), _ptr(pair_row), _ptr(out), out.stride(0),
+                                       _code(x.dtype), t, k, top, _stream()))
+        return out
+
     def linear(self, x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
                out_dtype: Optional[torch.dtype] = None, bias: Optional[torch.Tensor] = None,
                act: Optional[str] = None) -> torch.Tensor:
@@ -650,11 +828,18 @@ class Ops:
         return out
 
     def rope_kv_write(self, q, k, v, pos, req, freqs, k_pages, v_pages, block_table,
-                      page_size: int, n_heads: int, n_kv_heads: int, head_dim: int, v_freqs=None) -> None:
+                      page_size: int, n_heads: int, n_kv_heads: int, head_dim: int, v_freqs=None, qk_norm=None) -> None:
         """Rotate ``q`` in place; rotate ``k`` and copy ``v`` into their pages (``v`` is
         rotated too, by the table ``v_freqs``, when that is given).
         ``q``/``k``/``v`` are row-strided views [T, heads*head_dim]; ``k``/``v``
-        may both be ``None`` (queries only)."""
+        may both be ``None`` (queries only).  ``qk_norm`` = (rstd [T, 2], query weights, key
+        weights), all float32: queries and keys are multiplied by their token's factor (see
+        ``qk_rstd``) and their weights before they turn."""
+        rstd, qn_w, kn_w = qk_norm if qk_norm is not None else (None, None, None)
+        if rstd is not None:
+            assert rstd.dtype == torch.float32 and rstd.is_contiguous() and rstd.shape == (q.shape[0], 2)
+            assert qn_w.dtype == torch.float32 and qn_w.numel() == n_heads * head_dim and qn_w.is_contiguous()
+            assert k is None or (kn_w.dtype == torch.float32 and kn_w.numel() == n_kv_heads * head_dim)
         t = q.shape[0]
         assert q.stride(1) == 1 and pos.dtype == torch.int32 and req.dtype == torch.int32
         if k is not None:
@@ -671,7 +856,21 @@ class Ops:
             _ptr(freqs), _ptr(v_freqs) if k is not None else None, _ptr(k_pages) if k is not None else None,
             _ptr(v_pages) if k is not None else None,
             _ptr(block_table) if k is not None else None, width, page_size, n_pages,
-            t, n_heads, n_kv_heads, head_dim, _ptr(self.status), _stream()))
+            t, n_heads, n_kv_heads, head_dim, _ptr(self.status), _ptr(rstd), _ptr(qn_w), _ptr(kn_w), _stream()))
+
+    def qk_rstd(self, q, k, count_q: int, count_k: int, eps: float, req) -> torch.Tensor:
+        """For every token the factors of an RMS norm over its whole query projection and over its
+        whole key projection: ``rsqrt(sum(x^2) / count + eps)`` as float32 [T, 2].  ``q`` / ``k`` are
+        row-strided views whose padding columns hold zeros; ``count`` is the number of real ones.
+        ``k`` may be ``None``."""
+        t = q.shape[0]
+        assert q.stride(1) == 1 and (k is None or (k.stride(1) == 1 and k.dtype == q.dtype))
+        out = torch.empty((t, 2), dtype=torch.float32, device=q.device)
+        _check(self.lib, self.lib.fg_qk_rstd(
+            _ptr(q), q.stride(0), q.shape[1], int(count_q), _ptr(k), k.stride(0) if k is not None else 0,
+            k.shape[1] if k is not None else 0, int(count_k), _code(q.dtype), _ptr(req), float(eps), _ptr(out), t,
+            _stream()))
+        return out
 
     def _decode_scratch(self, floats: int) -> torch.Tensor:
         """Scratch for the split partials.  Buffers are kept for good (captured
@@ -719,7 +918,7 @@ class Ops:
 
     def attention(self, q, out, memory, ctx, n_heads: int, n_kv_heads: int, head_dim: int,
                   window: Optional[int], scale: float, out_freqs: Optional[torch.Tensor] = None,
-                  keep_first: int = 0) -> bool:
+                  keep_first: int = 0, softcap: Optional[float] = None) -> bool:
         """Paged causal attention of the step's query tokens; ``memory`` is the
         run's :class:`~fastgen_b200.cache.LayerMemory`, ``ctx`` the step's
         context.  bfloat16 runs on the tensor cores: prompt portions in one
@@ -729,7 +928,9 @@ class Ops:
         ``out_freqs`` (a frequency table, or ``None``): the caller wants the outputs' adjacent
         pairs turned by ``position * frequency``.  Returns ``True`` if the kernels did that for
         every token of the step (a bfloat16 step of single tokens only: the merge of the splits
-        turns what it stores), ``False`` if the caller still has to (``rotate_heads``)."""
+        turns what it stores), ``False`` if the caller still has to (``rotate_heads``).
+
+        ``softcap``: a scaled score ``s`` enters the softmax as ``softcap * tanh(s / softcap)``."""
         lib = attn(head_dim)
         k_pages, v_pages, block_table, page_size = (
             memory.k_pages, memory.v_pages, memory.block_table, memory.page_size)
@@ -742,13 +943,14 @@ class Ops:
             _check(lib, lib.fg_attention_simt(
                 _ptr(q), q.stride(0), _ptr(out), out.stride(0), _code(q.dtype), *common,
                 _ptr(tiles.req), _ptr(tiles.tok0), _ptr(tiles.ntok), tiles.n,
-                n_heads, n_kv_heads, head_dim, int(window or 0), keep_first, float(scale),
+                n_heads, n_kv_heads, head_dim, int(window or 0), keep_first, float(scale), float(softcap or 0.0),
                 _ptr(self.status), _stream()))
             return False
         # windows that keep a sequence's first positions visible run on the mma.sync kernels (on TMA
         # tiles for prompts where the pools have tensor maps), which walk the tiles of the kept
         # positions before those of the window
-        use_tma = memory.tensor_maps is not None
+        # capped scores: the cap lives in the mma.sync kernels on cp.async tiles
+        use_tma = memory.tensor_maps is not None and not softcap
         rows = PREFILL_TMA_ROWS if use_tma else PREFILL_ROWS
         tiling = attention_tiling(n_heads, n_kv_heads, rows)
         tiles = ctx.attention_tiles(tiling, 2)
@@ -774,7 +976,7 @@ class Ops:
             _check(lib, lib.fg_attention_prefill_bf16(
                 _ptr(q), q.stride(0), _ptr(out), out.stride(0), *common,
                 _ptr(tiles.req), _ptr(tiles.tok0), _ptr(tiles.ntok), tiles.n,
-                n_heads, n_kv_heads, head_dim, int(window or 0), keep_first, float(scale),
+                n_heads, n_kv_heads, head_dim, int(window or 0), keep_first, float(scale), float(softcap or 0.0),
                 _ptr(self.status), _stream()))
         singles = ctx.single_tokens()
         fused = out_freqs is not None and tiles.n == 0 and singles.n > 0
@@ -801,8 +1003,8 @@ class Ops:
                     _ptr(self.status), _stream()))
             else:
                 _check(lib, lib.fg_attention_decode_bf16(
-                    _ptr(q), q.stride(0), _ptr(out), out.stride(0), *common, *head, turn, _ptr(self.status),
-                    _stream()))
+                    _ptr(q), q.stride(0), _ptr(out), out.stride(0), *common, *head, turn, float(softcap or 0.0),
+                    _ptr(self.status), _stream()))
             Ops.launches += 1  # the combine kernel
         return fused
 

@@ -53,7 +53,8 @@ rope_kv_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_s
                const int* __restrict__ req, const float* __restrict__ freqs,
                const float* __restrict__ v_freqs, T* __restrict__ k_pages, T* __restrict__ v_pages, const int* __restrict__ block_table, int table_width,
                int page_size, int n_pages, int n_heads, int n_kv_heads, int head_dim, int* status,
-               bool vec, int heads_per_block) {
+               bool vec, int heads_per_block, const float* rstd, const float* __restrict__ qn_w,
+               const float* __restrict__ kn_w) {
   const int t = blockIdx.x;
   const int r = req[t];
   if (r < 0) return;
@@ -66,6 +67,8 @@ rope_kv_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_s
   const int total = n_heads + 2 * n_kv;  // heads in the order q..., k..., v...
   const int h_end = min(total, (int)(blockIdx.y + 1) * heads_per_block);
   float s = 0.f, c = 1.f, sv = 0.f, cv = 1.f;
+  // queries and keys normed over their whole projection: the token's two factors
+  const float rq = rstd ? rstd[2 * t] : 1.f, rk = rstd ? rstd[2 * t + 1] : 1.f;
   if (freqs != nullptr) sincosf((float)p * freqs[j], &s, &c);
   if (v_freqs != nullptr) sincosf((float)p * v_freqs[j], &sv, &cv);
   size_t slot = 0;
@@ -73,7 +76,11 @@ rope_kv_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_s
   for (int h = blockIdx.y * heads_per_block + lane_head; h < h_end; h += lanes) {
     if (h < n_heads) {
       T* x = q + (size_t)t * q_stride + h * head_dim + 2 * j;
-      const float2 val = load_pair<T>(x, vec);
+      float2 val = load_pair<T>(x, vec);
+      if (rstd != nullptr) {
+        val.x *= rq * qn_w[h * head_dim + 2 * j];
+        val.y *= rq * qn_w[h * head_dim + 2 * j + 1];
+      }
       store_pair<T>(x, make_float2(val.x * c - val.y * s, val.y * c + val.x * s), vec);
       continue;
     }
@@ -97,7 +104,11 @@ rope_kv_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_s
       store_pair<T>(v_pages + dst, make_float2(val.x * cv - val.y * sv, val.y * cv + val.x * sv), vec);
     } else {
       const T* x = k + (size_t)t * k_stride + g * head_dim + 2 * j;
-      const float2 val = load_pair<T>(x, vec);
+      float2 val = load_pair<T>(x, vec);
+      if (rstd != nullptr) {
+        val.x *= rk * kn_w[g * head_dim + 2 * j];
+        val.y *= rk * kn_w[g * head_dim + 2 * j + 1];
+      }
       store_pair<T>(k_pages + dst, make_float2(val.x * c - val.y * s, val.y * c + val.x * s), vec);
     }
   }
@@ -114,7 +125,8 @@ rope_kv_bf16x8_kernel(__nv_bfloat16* __restrict__ q, int q_stride, const __nv_bf
                       const int* __restrict__ req, const float* __restrict__ freqs,
                       const float* __restrict__ v_freqs, __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages,
                       const int* __restrict__ block_table, int table_width, int page_size, int n_pages,
-                      int n_heads, int n_kv_heads, int head_dim, int* status, int heads_per_block) {
+                      int n_heads, int n_kv_heads, int head_dim, int* status, int heads_per_block,
+                      const float* rstd, const float* __restrict__ qn_w, const float* __restrict__ kn_w) {
   const int t = blockIdx.x;
   const int r = req[t];
   if (r < 0) return;
@@ -144,11 +156,17 @@ rope_kv_bf16x8_kernel(__nv_bfloat16* __restrict__ q, int q_stride, const __nv_bf
     }
     slot = (size_t)page * n_kv_heads * page_size + (p - logical * page_size);
   }
-  auto rotate = [&](uint4 raw) {
+  const float rq = rstd ? rstd[2 * t] : 1.f, rk = rstd ? rstd[2 * t + 1] : 1.f;
+  // nw: the eight norm weights of this piece of the head (null: no norm), r: the token's factor
+  auto rotate = [&](uint4 raw, const float* nw, float r) {
     __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&raw);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const float2 val = __bfloat1622float2(h2[i]);
+      float2 val = __bfloat1622float2(h2[i]);
+      if (nw != nullptr) {
+        val.x *= r * nw[2 * i];
+        val.y *= r * nw[2 * i + 1];
+      }
       h2[i] = __floats2bfloat162_rn(val.x * cs[i] - val.y * sn[i], val.y * cs[i] + val.x * sn[i]);
     }
     return raw;
@@ -180,16 +198,61 @@ rope_kv_bf16x8_kernel(__nv_bfloat16* __restrict__ q, int q_stride, const __nv_bf
       const int h = h0 + u * lanes;
       if (h >= h_end) continue;
       if (h < n_heads) {
-        *reinterpret_cast<uint4*>(q + (size_t)t * q_stride + h * head_dim + piece * 8) = rotate(raw[u]);
+        *reinterpret_cast<uint4*>(q + (size_t)t * q_stride + h * head_dim + piece * 8) =
+            rotate(raw[u], rstd ? qn_w + h * head_dim + piece * 8 : nullptr, rq);
         continue;
       }
       const bool is_v = h >= n_heads + n_kv;
       const int g = h - n_heads - (is_v ? n_kv : 0);
       const size_t dst = (slot + (size_t)g * page_size) * head_dim + piece * 8;
       *reinterpret_cast<uint4*>((is_v ? v_pages : k_pages) + dst) =
-          is_v ? (v_freqs != nullptr ? rotate_v(raw[u]) : raw[u]) : rotate(raw[u]);
+          is_v ? (v_freqs != nullptr ? rotate_v(raw[u]) : raw[u])
+               : rotate(raw[u], rstd ? kn_w + g * head_dim + piece * 8 : nullptr, rk);
     }
   }
+}
+
+// The factors of a norm of queries and keys over their whole projection: for every token
+// out[2t] = rsqrt(sum of squares of its nq query columns / count_q + eps) and out[2t+1] the same of
+// its nk key columns (count: the columns that are not padding; padding columns hold zeros).
+template <typename T>
+__global__ void __launch_bounds__(128)
+qk_rstd_kernel(const T* q, long q_stride, int nq, float count_q, const T* k, long k_stride, int nk, float count_k,
+               const int* __restrict__ req, float eps, float* __restrict__ out) {
+  __shared__ float scratch[32];
+  const int t = blockIdx.x;
+  if (req[t] < 0) return;
+  float sq = 0.f, sk = 0.f;
+  for (int d = threadIdx.x; d < nq; d += blockDim.x) {
+    const float v = to_f32<T>(q[(size_t)t * q_stride + d]);
+    sq = fmaf(v, v, sq);
+  }
+  for (int d = threadIdx.x; d < nk; d += blockDim.x) {
+    const float v = to_f32<T>(k[(size_t)t * k_stride + d]);
+    sk = fmaf(v, v, sk);
+  }
+  sq = block_sum(sq, scratch);
+  sk = block_sum(sk, scratch);
+  if (threadIdx.x == 0) {
+    out[2 * t] = rsqrtf(sq / count_q + eps);
+    out[2 * t + 1] = nk > 0 ? rsqrtf(sk / count_k + eps) : 1.f;
+  }
+}
+
+extern "C" int fg_qk_rstd(const void* q, long q_stride, int nq, int count_q, const void* k, long k_stride, int nk,
+                          int count_k, int dtype, const int* req, float eps, float* out, int n_tokens,
+                          cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  FG_CHECK_ARG(nq > 0 && count_q > 0 && (nk == 0 || (k != nullptr && count_k > 0)), "fg_qk_rstd: bad sizes");
+  if (dtype == FG_F32)
+    qk_rstd_kernel<float><<<n_tokens, 128, 0, stream>>>((const float*)q, q_stride, nq, (float)count_q, (const float*)k,
+                                                        k_stride, nk, (float)count_k, req, eps, out);
+  else
+    qk_rstd_kernel<__nv_bfloat16><<<n_tokens, 128, 0, stream>>>((const __nv_bfloat16*)q, q_stride, nq, (float)count_q,
+                                                                (const __nv_bfloat16*)k, k_stride, nk, (float)count_k,
+                                                                req, eps, out);
+  FG_CHECK_LAUNCH("fg_qk_rstd");
+  return 0;
 }
 
 // q: [T, n_heads*head_dim] with row stride q_stride (elements), rotated in place.
@@ -201,8 +264,10 @@ extern "C" int fg_rope_kv_write(void* q, int q_stride, const void* k, int k_stri
                                 const float* freqs, const float* v_freqs, void* k_pages, void* v_pages,
                                 const int* block_table, int table_width, int page_size, int n_pages,
                                 int n_tokens, int n_heads, int n_kv_heads, int head_dim, int* status,
-                                cudaStream_t stream) {
+                                const float* rstd, const float* qn_w, const float* kn_w, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
+  FG_CHECK_ARG(rstd == nullptr || (qn_w != nullptr && (k == nullptr || kn_w != nullptr)),
+               "fg_rope_kv_write: a norm of queries and keys needs its weights");
   FG_CHECK_ARG(head_dim > 0 && head_dim % 2 == 0, "fg_rope_kv_write: head_dim %d must be even", head_dim);
   FG_CHECK_ARG((k == nullptr) == (v == nullptr), "fg_rope_kv_write: k and v must both be given or both null");
   FG_CHECK_ARG(k == nullptr || (k_pages && v_pages && block_table && page_size > 0),
@@ -225,7 +290,7 @@ extern "C" int fg_rope_kv_write(void* q, int q_stride, const void* k, int k_stri
     rope_kv_bf16x8_kernel<<<grid, threads, 0, stream>>>(
         (__nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v, v_stride, pos, req,
         freqs, v_freqs, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, block_table, table_width, page_size,
-        n_pages, n_heads, n_kv_heads, head_dim, status, ipt);
+        n_pages, n_heads, n_kv_heads, head_dim, status, ipt, rstd, qn_w, kn_w);
     FG_CHECK_LAUNCH("fg_rope_kv_write");
     return 0;
   }
@@ -233,12 +298,12 @@ extern "C" int fg_rope_kv_write(void* q, int q_stride, const void* k, int k_stri
     rope_kv_kernel<float><<<grid, threads, 0, stream>>>(
         (float*)q, q_stride, (const float*)k, k_stride, (const float*)v, v_stride, pos, req, freqs, v_freqs,
         (float*)k_pages, (float*)v_pages, block_table, table_width, page_size, n_pages, n_heads,
-        n_kv_heads, head_dim, status, vec, ipt);
+        n_kv_heads, head_dim, status, vec, ipt, rstd, qn_w, kn_w);
   else if (dtype == FG_BF16)
     rope_kv_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
         (__nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v,
         v_stride, pos, req, freqs, v_freqs, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, block_table,
-        table_width, page_size, n_pages, n_heads, n_kv_heads, head_dim, status, vec, ipt);
+        table_width, page_size, n_pages, n_heads, n_kv_heads, head_dim, status, vec, ipt, rstd, qn_w, kn_w);
   else
     FG_CHECK_ARG(false, "fg_rope_kv_write: bad dtype %d", dtype);
   FG_CHECK_LAUNCH("fg_rope_kv_write");

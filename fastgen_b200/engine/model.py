@@ -18,8 +18,10 @@ from ..parts.base import (
     Block,
     CacheSpec,
     Embedder,
+    Part,
     StateSpec,
     WeightSpec,
+    ScaledSum,
     StreamUpdate,
     make_block,
     make_connection,
@@ -51,6 +53,7 @@ def _build_blocks(args: ModelArgs) -> List[Block]:
                 make_norm(layer.mixer_norm),
                 make_feed_forward(layer.ffn) if layer.ffn is not None else None,
                 make_norm(layer.ffn_norm) if layer.ffn_norm is not None else None,
+                params=layer.block_params,
                 **extra,
             )
         )
@@ -71,6 +74,8 @@ def _collect_specs(args: ModelArgs, blocks: Sequence[Block], final_norm, embedde
         for part in block.parts():
             ordered.extend(part.weight_specs())
     ordered.extend(final_norm.weight_specs())
+    if args.step_table_name is not None:
+        ordered.append(WeightSpec(args.step_table_name, (args.step_table_rows, args.dim), ("normal", 0.1)))
     if not args.tie_embeddings:
         ordered.append(WeightSpec(args.output_name, (args.vocab_size, args.dim)))
     for s in ordered:
@@ -96,6 +101,7 @@ class Model:
         self.embedder = _build_embedder(args)
         self.embedding: Optional[torch.Tensor] = None
         self.output: Optional[torch.Tensor] = None
+        self.step_table: Optional[torch.Tensor] = None  # float32 [rows, dim]
 
     # -- description -----------------------------------------------------------
     def weight_specs(self) -> List[WeightSpec]:
@@ -129,15 +135,18 @@ class Model:
             if t is not None and t.data_ptr() not in seen:
                 seen.add(t.data_ptr())
                 total += t.numel() * t.element_size()
+        def add_part(part):
+            for v in vars(part).values():
+                if isinstance(v, torch.Tensor):
+                    add(v)
+                elif isinstance(v, Part):  # a part made of parts (two mixers side by side)
+                    add_part(v)
         add(self.output)
+        add(self.step_table)
         for block in self.blocks:
             for part in block.parts():
-                for v in vars(part).values():
-                    if isinstance(v, torch.Tensor):
-                        add(v)
-        for v in vars(self.final_norm).values():
-            if isinstance(v, torch.Tensor):
-                add(v)
+                add_part(part)
+        add_part(self.final_norm)
         return total
 
     # -- weights -----------------------------------------------------------------
@@ -155,6 +164,9 @@ class Model:
         self.final_norm.bind(
             {local: tensors[name] for local, name in self.final_norm.names.items()}, self.ops
         )
+        if self.args.step_table_name is not None:
+            # the vectors join the float32 residual sum: float32 whatever they were stored in
+            self.step_table = tensors[self.args.step_table_name].float().contiguous()
 
     @staticmethod
     def load(model_dir, dtype: torch.dtype, device) -> "Model":
@@ -211,6 +223,9 @@ class Model:
         self.embedder.forward(ctx, getattr(memories, "embedder_state", None), h)
         pending = None
         for e, entry in enumerate(self.args.schedule):
+            if entry.step_row is not None:
+                # the pass's step vector joins whatever the layer before left pending
+                pending = ScaledSum.of(pending).plus(ScaledSum([], row=self.step_table[entry.step_row]))
             h, pending = self.blocks[entry.layer].forward(h, pending, ctx, memories[e])
         if ctx.n_want == 0:
             return None

@@ -53,7 +53,8 @@ class GQAAttention(Mixer):
     cache pages before attention reads them back, so a prompt portion attends to
     itself through the cache exactly as a decoded token does.
 
-    Options of the parameters: biases on the four projections; a value head size of its own
+    Options of the parameters: biases on the four projections; an RMS norm of queries and of keys
+    over their whole projection before the rotation; a cap on the scores; a value head size of its own
     (heads are padded with zero rows to one kernel head size, see
     ``AttentionParams.kernel_head_dim``); rotary encodings that turn a part of the head, in
     either pairing (half-split rows are reordered at bind time, which changes no score);
@@ -91,6 +92,11 @@ class GQAAttention(Mixer):
                 WeightSpec(self.names["bk"], (k,)),
                 WeightSpec(self.names["bv"], (v,)),
                 WeightSpec(self.names["bo"], (p.dim,)),
+            ]
+        if p.qk_norm:
+            specs += [
+                WeightSpec(self.names["q_norm"], (q,), ("ones",)),
+                WeightSpec(self.names["k_norm"], (k,), ("ones",)),
             ]
         return specs
 
@@ -130,6 +136,12 @@ class GQAAttention(Mixer):
             bv = self._rows(tensors["bv"], p.n_kv_heads, vd, p.v_layout, self.value_position)
             self.bqkv = torch.cat([bq, bk, bv], dim=0).to(dt).contiguous()
             self.bo = tensors["bo"].to(dt).contiguous()
+        self.q_norm = self.k_norm = None
+        if p.qk_norm:
+            # the norm's weights follow their projection's rows (a head's padding has weight zero);
+            # they enter float32 arithmetic
+            self.q_norm = self._rows(tensors["q_norm"], p.n_heads, p.head_dim, p.qk_layout, qk_pos).float().contiguous()
+            self.k_norm = self._rows(tensors["k_norm"], p.n_kv_heads, p.head_dim, p.qk_layout, qk_pos).float().contiguous()
         self.freqs = self._table(self.position)
         self.v_freqs = self.v_unfreqs = None
         if self.value_position is not None:
@@ -150,13 +162,13 @@ class GQAAttention(Mixer):
         back already (values cached turned by their positions): the kernels do it where they can."""
         p = self.params
         return self.ops.attention(q, o, memory, ctx, p.n_heads, p.n_kv_heads, self.hd, p.window, self.scale,
-                                  out_freqs=self.v_unfreqs, keep_first=p.keep_first)
+                                  out_freqs=self.v_unfreqs, keep_first=p.keep_first, softcap=p.softcap)
 
     def forward(self, x, ctx, memory):
         p, ops = self.params, self.ops
         t = x.shape[0]
         q = None
-        if memory.writes and x.dtype == torch.bfloat16:
+        if memory.writes and x.dtype == torch.bfloat16 and not p.qk_norm:
             # a few tokens: projection, rotation and page write in one kernel
             q = ops.qkv_rope_write(x, self.wqkv, ctx.pos, ctx.req, self.freqs, memory,
                                    p.n_heads, p.n_kv_heads, self.hd, bias=self.bqkv, v_freqs=self.v_freqs)
@@ -171,9 +183,16 @@ class GQAAttention(Mixer):
                 bq = self.bqkv[: self.q_width] if self.bqkv is not None else None
                 q = ops.linear(x, self.wqkv[: self.q_width], bias=bq)
                 k = v = None
+            qk_norm = None
+            if p.qk_norm:
+                # a norm over the whole projection: the token's two factors first, then the kernel
+                # that rotates multiplies by them and by the weights
+                rstd = ops.qk_rstd(q, k, p.n_heads * p.head_dim, p.n_kv_heads * p.head_dim, p.qk_norm_eps, ctx.req)
+                qk_norm = (rstd, self.q_norm, self.k_norm)
             ops.rope_kv_write(
                 q, k, v, ctx.pos, ctx.req, self.freqs, memory.k_pages, memory.v_pages,
                 memory.block_table, memory.page_size, p.n_heads, p.n_kv_heads, self.hd, v_freqs=self.v_freqs,
+                qk_norm=qk_norm,
             )
         o = torch.empty((t, self.q_width), dtype=x.dtype, device=x.device)
         turned = self._attend(q, o, ctx, memory)

@@ -25,7 +25,9 @@ class WeightSpec:
     ``("normal", std)``, ``("ones",)``, ``("ones_jitter", half_width)`` for
     ``1 + U(-w, w)``, or ``("randint", high)`` for integer tables.
     ``integer`` tensors are kept as int32; others follow the compute dtype
-    unless the file stores them in 32-bit (see ``weights.loader``).
+    unless the file stores them in 32-bit (see ``weights.loader``).  A size of -1 in
+    ``shape`` stands for "whatever the checkpoint has" (the part reads it when it binds);
+    the random-weights writer needs every size.
     """
 
     name: str
@@ -88,6 +90,17 @@ class Part:
 
 
 class Norm(Part):
+    def _joined(self, h, total, rows):
+        """For norms whose kernel does not take a :class:`ScaledSum`: add it to ``h`` with the kernel
+        that does (needs ``self.ops``) and return ``None``; with ``rows`` (``h`` must stay as it
+        was) the sum is formed beside ``h`` and returned as the one summand."""
+        if rows is None:
+            total.add_into(h, self.ops)
+            return None
+        delta = torch.zeros_like(h)
+        total.add_into(delta, self.ops)
+        return delta
+
     def forward(self, x: torch.Tensor, out_dtype=None, rows=None) -> torch.Tensor:
         """Normalise rows of ``x`` [T, dim] (only the rows indexed by the int32
         tensor ``rows`` when it is given)."""
@@ -102,6 +115,8 @@ class Norm(Part):
         be left as it was.
 
         The default composes the steps; implementations may fuse them."""
+        if isinstance(delta, ScaledSum):
+            delta = self._joined(h, delta, rows)
         if delta is not None:
             if delta_norm is not None:
                 delta = delta_norm.forward(delta, out_dtype=torch.float32)
@@ -110,6 +125,43 @@ class Norm(Part):
                 return self.forward(h)
             h.add_(delta.to(h.dtype))
         return self.forward(h, rows=rows)
+
+
+@dataclass
+class ScaledSum:
+    """A sum that has not been formed yet: ``row + sum_i coef_i * term_i`` with ``terms`` a list of
+    ``(tensor [T, dim], coef)`` and ``row`` a float32 [dim] vector that joins every token (or
+    ``None``).  Blocks whose sub-layers read one norm side by side hand it on as ``pending``, so
+    that one kernel adds everything to the residual stream and norms the result."""
+
+    terms: list
+    row: Optional[torch.Tensor] = None
+
+    @staticmethod
+    def of(pending, coef: float = 1.0) -> "ScaledSum":
+        """``coef * pending`` as a sum: a tensor becomes its one term, a sum is multiplied through."""
+        if pending is None:
+            return ScaledSum([])
+        if isinstance(pending, ScaledSum):
+            if pending.row is not None and coef != 1.0:
+                raise ValueError("a sum with a row vector cannot be multiplied")
+            return ScaledSum([(t, c * coef) for t, c in pending.terms], pending.row)
+        if isinstance(pending, torch.Tensor):
+            return ScaledSum([(pending, coef)])
+        raise TypeError(f"{type(pending).__name__} cannot join a scaled sum")
+
+    def plus(self, other: "ScaledSum") -> "ScaledSum":
+        if self.row is not None and other.row is not None:
+            raise ValueError("two row vectors in one sum")
+        return ScaledSum(self.terms + other.terms, self.row if self.row is not None else other.row)
+
+    def add_into(self, h: torch.Tensor, ops) -> None:
+        """``h += the sum`` (no norm): for norms whose own kernel does not take such a sum."""
+        terms = list(self.terms)
+        row = self.row
+        while terms or row is not None:
+            ops.rmsnorm_sum(h, terms[:4], None, 0.0, row=row)
+            terms, row = terms[4:], None
 
 
 @dataclass
@@ -210,7 +262,9 @@ class Block:
     """Arrangement of a layer's parts around the residual stream."""
 
     def __init__(self, mixer: Mixer, mixer_norm: Norm, ffn: Optional[FeedForward], ffn_norm: Optional[Norm],
-                 **extra: Part):
+                 params=None, **extra: Part):
+        #: the arrangement's own constants (``LayerSpec.block_params``), or ``None``
+        self.params = params
         self.mixer = mixer
         self.mixer_norm = mixer_norm
         self.ffn = ffn
@@ -299,8 +353,10 @@ def make_position(spec: PartSpec) -> PositionEncoding:
     return _make(_POSITIONS, "position encoding", spec)
 
 
-def make_block(kind: str, mixer, mixer_norm, ffn, ffn_norm, **extra) -> Block:
+def make_block(kind: str, mixer, mixer_norm, ffn, ffn_norm, params=None, **extra) -> Block:
     factory = _BLOCKS.get(kind)
     if factory is None:
         raise KeyError(f"no block of kind {kind!r} is registered; known: {sorted(_BLOCKS)}")
+    if params is not None:
+        extra["params"] = params
     return factory(mixer, mixer_norm, ffn, ffn_norm, **extra)

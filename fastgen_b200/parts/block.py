@@ -2,7 +2,7 @@
 
 from __future__ import annotations
 
-from .base import Block, NormedDelta, register_block, split_pending
+from .base import Block, NormedDelta, ScaledSum, register_block, split_pending
 
 
 class PreNormBlock(Block):
@@ -60,6 +60,24 @@ class StreamsBlock(Block):
         return h, c.write(self.ffn.forward(c.read(h, pending, self.ffn_norm), ctx))
 
 
+class ParallelBlock(Block):
+    """One norm, read by every sub-layer: ``h = h + m * (mixer(norm(h)) + ffn(norm(h)))`` with ``m``
+    the ``residual_mult`` of the block's parameters.  The sub-layers' outputs stay apart (a
+    :class:`ScaledSum`) until the next norm, whose kernel multiplies each by its factor in float32,
+    adds them to the residual stream and norms the result.  A layer without a feed-forward adds the
+    mixer alone."""
+
+    def forward(self, h, pending, ctx, memory):
+        mult = self.params.residual_mult if self.params is not None else 1.0
+        delta, delta_norm = split_pending(pending)
+        a = self.mixer_norm.add_forward(h, delta, delta_norm=delta_norm)
+        out = ScaledSum.of(self.mixer.forward(a, ctx, memory), mult)
+        if self.ffn is not None:
+            out = out.plus(ScaledSum.of(self.ffn.forward(a, ctx), mult))
+        return h, out
+
+
 register_block("prenorm", PreNormBlock)
+register_block("parallel", ParallelBlock)
 register_block("streams", StreamsBlock)
 register_block("sandwich", SandwichBlock)

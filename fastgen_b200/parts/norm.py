@@ -6,7 +6,7 @@ from typing import List
 
 import torch
 
-from .base import Norm, StreamUpdate, WeightSpec, register_norm
+from .base import Norm, ScaledSum, StreamUpdate, WeightSpec, register_norm
 from .params import DynamicTanhParams, LayerNormParams, RMSNormParams
 
 
@@ -20,7 +20,8 @@ class RMSNorm(Norm):
     params: RMSNormParams
 
     def weight_specs(self) -> List[WeightSpec]:
-        return [WeightSpec(self.names["weight"], (self.params.dim,), ("ones",))]
+        init = ("normal", 0.1) if self.params.one_plus else ("ones",)
+        return [WeightSpec(self.names["weight"], (self.params.dim,), init)]
 
     def bind(self, tensors, ops) -> None:
         self.ops = ops
@@ -32,14 +33,25 @@ class RMSNorm(Norm):
     def forward(self, x, out_dtype=None, rows=None):
         n = x.shape[0] if rows is None else rows.numel()
         out = torch.empty((n, x.shape[1]), dtype=out_dtype or self.ops.act_dtype, device=x.device)
+        if self.params.one_plus:
+            # the factor 1 + w is formed in float32 by the kernel that also takes sums of summands
+            return self.ops.rmsnorm_sum(x, (), self.weight, self.params.eps, out=out, rows=rows, one_plus=True)
         return self.ops.rmsnorm(x, self.weight, self.params.eps, out=out, rows=rows)
 
     def add_forward(self, h, delta, rows=None, delta_norm=None):
-        """``h += delta`` in float32 (stored back unless ``rows`` gathers), then the norm."""
+        """``h += delta`` in float32 (stored back unless ``rows`` gathers), then the norm.  ``delta``
+        may be a :class:`ScaledSum`: all of its summands join in the same kernel."""
         if delta_norm is not None:
             return super().add_forward(h, delta, rows=rows, delta_norm=delta_norm)
         n = h.shape[0] if rows is None else rows.numel()
         out = torch.empty((n, h.shape[1]), dtype=self.ops.act_dtype, device=h.device)
+        if isinstance(delta, ScaledSum) or self.params.one_plus:
+            total = ScaledSum.of(delta)
+            if len(total.terms) > 4 or len({t.dtype for t, _ in total.terms}) > 1:
+                total.add_into(h, self.ops)
+                total = ScaledSum([])
+            return self.ops.rmsnorm_sum(h, total.terms, self.weight, self.params.eps, out=out, row=total.row,
+                                        rows=rows, one_plus=self.params.one_plus)
         return self.ops.rmsnorm(h, self.weight, self.params.eps, out=out, delta=delta, rows=rows)
 
 
@@ -80,6 +92,8 @@ class DynamicTanh(Norm):
         return self.ops.dyt(x, self.triple(), out, rows=rows)
 
     def add_forward(self, h, delta, rows=None, delta_norm=None):
+        if isinstance(delta, ScaledSum):
+            delta = self._joined(h, delta, rows)
         if delta is not None and delta_norm is not None and not isinstance(delta_norm, DynamicTanh):
             delta, delta_norm = delta_norm.forward(delta, out_dtype=torch.float32), None
         n = h.shape[0] if rows is None else rows.numel()
@@ -125,6 +139,8 @@ class LayerNorm(Norm):
         return self.streams_forward(x, rows=rows, out_dtype=out_dtype)
 
     def add_forward(self, h, delta, rows=None, delta_norm=None):
+        if isinstance(delta, ScaledSum):
+            delta = self._joined(h, delta, rows)
         if delta is not None and delta_norm is not None:
             delta = delta_norm.forward(delta, out_dtype=torch.float32)
         update = StreamUpdate(delta) if delta is not None else None

@@ -100,8 +100,19 @@ class AttentionParams:
     #: with a window: so many of a sequence's first positions stay visible to every later
     #: query, at their true positions
     keep_first: int = 0
+    #: ``"projection"``: queries and keys pass an RMS norm over their whole projection (all heads of
+    #: a token at once, eps ``qk_norm_eps``, plain weights ``q_norm`` / ``k_norm`` of that size) before
+    #: they are rotated; ``None``: none
+    qk_norm: Optional[str] = None
+    qk_norm_eps: float = 1e-6
+    #: a scaled score ``s`` enters the softmax as ``softcap * tanh(s / softcap)`` (``None``: as it is)
+    softcap: Optional[float] = None
 
     def __post_init__(self) -> None:
+        if self.qk_norm not in (None, "projection"):
+            raise ValueError(f"qk_norm must be None or 'projection', got {self.qk_norm!r}")
+        if self.softcap is not None and self.softcap <= 0:
+            raise ValueError(f"a cap on the scores must be positive, got {self.softcap}")
         for name, layout in (("qk_layout", self.qk_layout), ("v_layout", self.v_layout)):
             if layout not in ("adjacent", "half_split"):
                 raise ValueError(f"{name} must be 'adjacent' or 'half_split', got {layout!r}")
@@ -152,10 +163,12 @@ class SwiGLUParams:
 
 @dataclass(frozen=True)
 class RMSNormParams:
-    """``x * rsqrt(mean(x^2) + eps) * w`` (fastgen/kernels/rmsnorm.py:33-60)."""
+    """``x * rsqrt(mean(x^2) + eps) * w`` (fastgen/kernels/rmsnorm.py:33-60); with ``one_plus`` the
+    weight is stored around zero and the factor is ``1 + w``."""
 
     dim: int
     eps: float
+    one_plus: bool = False
 
 
 @dataclass(frozen=True)
@@ -290,3 +303,76 @@ class LatentAttentionParams:
             raise ValueError(f"the rotated part has {self.rot_dim} dimensions: a rotation needs pairs")
         if not 1 <= self.kv_rank <= 512:
             raise ValueError(f"the attention kernels take latents of 1 to 512 numbers, got {self.kv_rank}")
+
+
+@dataclass(frozen=True)
+class GatedDeltaParams:
+    """The gated delta rule: ``n_heads`` heads with a state of ``head_dim`` x ``v_head_dim`` each;
+    queries and keys have ``n_kv_heads`` heads (head ``h`` uses ``h // (n_heads / n_kv_heads)``).
+    q, k and v pass a causal convolution of ``conv`` taps per channel and SiLU.  The decay per head
+    and key channel and the gate of the output come through two low-rank maps whose inner sizes are
+    ``decay_rank`` and ``gate_rank`` (``None``: whatever the checkpoint's tensors have)."""
+
+    dim: int
+    n_heads: int
+    n_kv_heads: int
+    head_dim: int
+    v_head_dim: int
+    conv: int
+    eps: float
+    decay_rank: Optional[int] = None
+    gate_rank: Optional[int] = None
+
+    def __post_init__(self) -> None:
+        if self.n_heads % self.n_kv_heads:
+            raise ValueError(f"{self.n_heads} heads cannot share {self.n_kv_heads} query/key heads")
+        if not 1 <= self.conv <= 8:
+            raise ValueError(f"the convolution takes 1 to 8 taps, got {self.conv}")
+        if not 1 <= self.head_dim <= 256:
+            raise ValueError(f"the state takes 1 to 256 rows a head, got {self.head_dim}")
+
+    @property
+    def channels(self) -> int:
+        """Columns that pass the convolution: q, k and v."""
+        return 2 * self.n_kv_heads * self.head_dim + self.n_heads * self.v_head_dim
+
+
+@dataclass(frozen=True)
+class SideBySideParams:
+    """Two mixers that read the same input; the result is ``left_scale * left + right_scale * right``.
+    ``left`` and ``right`` are ``PartSpec``s of mixers; at most one of them caches per-token entries
+    and at most one keeps a fixed-size state (the layer's cache and state are theirs)."""
+
+    left: object
+    right: object
+    left_scale: float = 1.0
+    right_scale: float = 1.0
+
+
+@dataclass(frozen=True)
+class RoutedExpertsParams:
+    """``n_experts`` gated feed-forwards ``down(silu(gate x) * up x)`` of inner width ``ffn_dim``, of
+    which a token uses ``top``: the experts with the largest ``softmax(router x) + correction``
+    (``correction``: whether the model has that tensor), weighted by their softmax scores as they are
+    (``renormalize``: divided by their sum).  The router runs in float32."""
+
+    dim: int
+    ffn_dim: int
+    n_experts: int
+    top: int
+    correction: bool = True
+    renormalize: bool = False
+
+    def __post_init__(self) -> None:
+        if not 1 <= self.top <= self.n_experts:
+            raise ValueError(f"a token cannot use {self.top} of {self.n_experts} experts")
+        if self.n_experts > 256:
+            raise ValueError(f"the router takes up to 256 experts, got {self.n_experts}")
+
+
+@dataclass(frozen=True)
+class ParallelBlockParams:
+    """A layer whose sub-layers all read one norm: ``x <- x + residual_mult * (mixer(h) + ffn(h))``
+    with ``h = norm(x)``."""
+
+    residual_mult: float = 1.0

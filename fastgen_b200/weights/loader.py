@@ -53,6 +53,11 @@ def _kept_dtype(stored: torch.dtype, integer: bool) -> torch.dtype:
     return torch.bfloat16
 
 
+def _shape_fits(wanted: tuple, found: tuple) -> bool:
+    """Whether a stored shape is the one asked for; -1 in ``wanted`` takes any size."""
+    return len(wanted) == len(found) and all(w == -1 or w == f for w, f in zip(wanted, found))
+
+
 def load_weights(
     model_dir: Union[str, Path],
     specs: Sequence[WeightSpec],
@@ -82,7 +87,7 @@ def load_weights(
     wrong = [
         f"{n}: expected {tuple(wanted[n].shape)}, found {shapes[n]}"
         for n in sorted(wanted)
-        if n in shapes and tuple(wanted[n].shape) != shapes[n]
+        if n in shapes and not _shape_fits(tuple(wanted[n].shape), shapes[n])
     ]
     if missing or unexpected or wrong:
         lines = [f"checkpoint in {model_dir} does not match the model:"]

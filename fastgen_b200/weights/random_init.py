@@ -22,6 +22,8 @@ from ..parts.base import WeightSpec
 
 def draw(spec: WeightSpec, gen: torch.Generator, norm_jitter: float = 0.0) -> torch.Tensor:
     kind = spec.init[0]
+    if any(n < 0 for n in spec.shape):
+        raise ValueError(f"{spec.name}: the description leaves a size open ({spec.shape}); give it to draw the tensor")
     if kind == "normal":
         return torch.randn(spec.shape, generator=gen, dtype=torch.float32) * spec.init[1]
     if kind == "ones":

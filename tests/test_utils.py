@@ -43,15 +43,21 @@ def test_every_declared_signature_belongs_to_its_library():
     core = exported(build.CORE_SOURCES)
     attn = exported(["attention.cu"])
     latent = exported(["latent_mma.cu"])
+    delta = exported(["delta_rule.cu"])
+    moe = exported(["moe.cu"])
     assert set(ops._CORE_SIGNATURES) <= core, set(ops._CORE_SIGNATURES) - core
     assert set(ops._ATTN_SIGNATURES) <= attn, set(ops._ATTN_SIGNATURES) - attn
     assert set(ops._LATENT_SIGNATURES) <= latent, set(ops._LATENT_SIGNATURES) - latent
+    assert set(ops._DELTA_SIGNATURES) <= delta, set(ops._DELTA_SIGNATURES) - delta
+    assert set(ops._MOE_SIGNATURES) <= moe, set(ops._MOE_SIGNATURES) - moe
     # and every exported function that takes a pointer is declared
     called = set(re.findall(r"\blib\.(fg_\w+)\(", Path(ops.__file__).read_text()))
     undeclared = called - set(ops._CORE_SIGNATURES) - set(ops._ATTN_SIGNATURES) - set(ops._LATENT_SIGNATURES)
+    undeclared -= set(ops._DELTA_SIGNATURES) | set(ops._MOE_SIGNATURES)
     int_only = {"fg_attention_decode_scratch_floats", "fg_attention_decode_split", "fg_attention_prefill_rows",
                 "fg_attention_rows_per_block", "fg_last_error", "fg_attention_sigmoid_decode_keys",
-                "fg_latent_mma_rows", "fg_latent_mma_keys", "fg_latent_mma_scratch_floats"}
+                "fg_latent_mma_rows", "fg_latent_mma_keys", "fg_latent_mma_scratch_floats",
+                "fg_moe_gemm_tile_rows", "fg_moe_mma_tile_rows"}
     assert undeclared <= int_only, undeclared - int_only
 
 
