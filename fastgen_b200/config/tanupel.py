@@ -56,7 +56,9 @@ def _norm(dim: int, eps: float, name: str) -> PartSpec:
     return PartSpec("rmsnorm", RMSNormParams(dim, eps, one_plus=True), {"weight": name})
 
 
-def _rope(rot: Optional[Mapping[str, Any]], head_dim: int, where: str) -> PartSpec:
+def _rope(rot: Optional[Mapping[str, Any]], head_dim: int, where: str, by_wavelength: bool = True) -> PartSpec:
+    """``by_wavelength``: a scaling that names ``low``/``high``/``original`` bends the frequencies by
+    wavelength; without them, or with ``by_wavelength`` off, ``factor`` divides every frequency."""
     if not rot:
         return PartSpec("none", NoPositionParams())
     require(rot, ("dims", "base"), f"{where}.rot")
@@ -65,7 +67,7 @@ def _rope(rot: Optional[Mapping[str, Any]], head_dim: int, where: str) -> PartSp
     sc = rot.get("scaling")
     if sc:
         require(sc, ("factor",), f"{where}.rot.scaling")
-        if any(k in sc for k in ("low", "high", "original")):
+        if by_wavelength and any(k in sc for k in ("low", "high", "original")):
             require(sc, ("low", "high", "original"), f"{where}.rot.scaling")
             scaling = Llama3Scaling(float(sc["factor"]), float(sc["low"]), float(sc["high"]), sc["original"])
         else:
@@ -74,7 +76,8 @@ def _rope(rot: Optional[Mapping[str, Any]], head_dim: int, where: str) -> PartSp
                                        rot_dims=positive_int(rot, "dims"), linear_factor=linear))
 
 
-def _attention(dim: int, eps: float, m: Mapping[str, Any], prefix: str, where: str) -> PartSpec:
+def _attention(dim: int, eps: float, m: Mapping[str, Any], prefix: str, where: str,
+               by_wavelength: bool = True) -> PartSpec:
     require(m, ("heads", "kv_heads", "dim", "vdim", "scale"), where)
     head_dim = positive_int(m, "dim")
     softcap = m.get("softcap")
@@ -84,7 +87,7 @@ def _attention(dim: int, eps: float, m: Mapping[str, Any], prefix: str, where: s
         n_kv_heads=positive_int(m, "kv_heads"),
         head_dim=head_dim,
         v_head_dim=positive_int(m, "vdim"),
-        position=_rope(m.get("rot"), head_dim, where),
+        position=_rope(m.get("rot"), head_dim, where, by_wavelength),
         softmax_scale=float(m["scale"]),
         qk_layout="half_split",
         qk_norm="projection",
@@ -118,7 +121,8 @@ def _gated_delta(dim: int, eps: float, m: Mapping[str, Any], prefix: str, where:
 def _side_by_side(dim: int, eps: float, m: Mapping[str, Any], prefix: str, where: str) -> PartSpec:
     require(m, ("left", "right"), where)
     params = SideBySideParams(
-        left=_attention(dim, eps, m["left"], prefix + "left.", f"{where}.left"),
+        # the attention of a pair divides its frequencies by the factor, whatever else the scaling names
+        left=_attention(dim, eps, m["left"], prefix + "left.", f"{where}.left", by_wavelength=False),
         right=_gated_delta(dim, eps, m["right"], prefix + "right.", f"{where}.right"),
         left_scale=float(m.get("left_scale", 1.0)),
         right_scale=float(m.get("right_scale", 1.0)),

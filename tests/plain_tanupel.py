@@ -222,3 +222,25 @@ def forward(config, tensors: Dict[str, torch.Tensor], tokens, return_layers: boo
     if return_layers:
         return logits, torch.stack(after)
     return logits
+
+
+def read_model(model_dir, dtype=DT):
+    """``(config, tensors)`` of a model folder."""
+    import json
+    from pathlib import Path
+
+    from safetensors.torch import load_file
+
+    with open(Path(model_dir) / "config.json") as f:
+        config = json.load(f)
+    tensors = {k: v.to(dtype) for k, v in load_file(str(Path(model_dir) / "model.safetensors")).items()}
+    return config, tensors
+
+
+def greedy(config, tensors, prompt, n_new: int):
+    seq, out = list(prompt), []
+    for _ in range(n_new):
+        tok = int(forward(config, tensors, seq)[-1].argmax())
+        out.append(tok)
+        seq.append(tok)
+    return out
