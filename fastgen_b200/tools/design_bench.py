@@ -1,6 +1,6 @@
 """Throughput of one design beside another at equal size, step by step and kernel by kernel.
 
-``bench.py --design sinorax|zeladra`` runs this: prefill and decode throughput of a model of that
+``bench.py --design sinorax|zeladra|tanupel`` runs this: prefill and decode throughput of a model of that
 design at a few sizes that resemble a real model's layers (random weights), beside a Llama-shaped model of
 the same width, heads, head size, number of layers and number of parameters a layer, and the
 time of each kernel family of the two designs at those sizes with its fraction of the roofline
@@ -77,6 +77,30 @@ def zeladra_config(width, layers, heads, kv, head_dim, ffn, vocab, window) -> di
         out.append(dict(type=kind, mixer=mixer, mlp=dict(kind="dense", ff=ffn)))
     return dict(architecture="Zeladra", vocab=vocab, width=width, norm=dict(eps=1e-5), embedding=dict(scale=1.0),
                 streams=2, layers=out)
+
+
+def tanupel_config(width, layers, heads, kv, head_dim, ffn, vocab, window=None, experts=8, top=2) -> dict:
+    """A pair of mixers (capped attention with half the heads beside a gated delta rule with the
+    other half) and plain attention with the whole projection's query/key norm, in turn; the
+    feed-forwards are dense and routed in turn, the routed one with ``experts`` experts of
+    ``ffn / experts`` rows (as many parameters as the dense one, ``top`` of them a token).  All
+    layers are one run that is passed once, so the pass's step vector is added.  A layer has the
+    parameters of the Llama shape's layer, up to the small low-rank maps of the delta rule."""
+    rot = dict(dims=head_dim // 2, base=500000.0)
+    att = dict(heads=heads, kv_heads=kv, dim=head_dim, vdim=head_dim, scale=head_dim ** -0.5,
+               rot=dict(rot, scaling=dict(factor=8.0, low=1.0, high=4.0, original=8192)))
+    left = dict(heads=heads // 2, kv_heads=max(1, kv // 2), dim=head_dim, vdim=head_dim, scale=head_dim ** -0.5, softcap=30.0,
+                rot=dict(rot, scaling=dict(factor=4.0)))
+    right = dict(heads=heads // 2, kv_heads=max(1, kv // 2), dim=head_dim, vdim=head_dim, conv=4, decay_rank=32, gate_rank=32)
+    pair = dict(left=left, right=right, left_scale=0.6, right_scale=1.1)
+    dense = dict(kind="dense", ff=ffn)
+    routed = dict(kind="moe", expert=dict(ff=ffn // experts), router=dict(experts=experts, top=top))
+    out = []
+    for i in range(layers):
+        kind = ("parallel", "attention")[i % 2]
+        out.append(dict(type=kind, mixer=dict(pair if kind == "parallel" else att), mlp=dict(dense if (i // 2) % 2 == 0 else routed)))
+    return dict(architecture="Tanupel", vocab=vocab, width=width, norm=dict(eps=1e-5), embedding=dict(scale=1.0),
+                residual_mult=0.5, loop=dict(start=0, stop=layers, times=1), layers=out)
 
 
 class Timer:
@@ -196,7 +220,7 @@ def model_throughput(cfg, device) -> Dict[str, float]:
     return out
 
 
-def _attention_times(cfg, device, timer: Timer, layer: int, flops_window, heads, kv, head_dim) -> Dict[str, float]:
+def _attention_times(cfg, device, timer: Timer, layer: int, flops_window, heads, kv, head_dim, pick=None) -> Dict[str, float]:
     """The attention launches of one layer alone: a 2,048-token prompt, and 8 single tokens at
     position 2,048, with what the mixer adds around them (turning the outputs back)."""
     from ..engine import StepEntry
@@ -204,6 +228,8 @@ def _attention_times(cfg, device, timer: Timer, layer: int, flops_window, heads,
     engine = _engine(cfg, device, DECODE_BATCH, DECODE_CONTEXT)
     _fill(engine)
     mixer = engine.model.blocks[layer].mixer
+    if pick is not None:
+        mixer = pick(mixer)
     memory = engine.memories[layer]
     out = {}
     gen = torch.Generator().manual_seed(SEED)
@@ -300,7 +326,7 @@ def kernel_table(size, device, peaks) -> Dict[str, dict]:
     return table
 
 
-def _mixer_times(cfg, device, timer: Timer, layer: int) -> Dict[str, float]:
+def _mixer_times(cfg, device, timer: Timer, layer: int, pick=None) -> Dict[str, float]:
     """A whole mixer of one layer alone (its projections included): a 2,048-token prompt, and 8
     single tokens at position 2,048."""
     from ..engine import StepEntry
@@ -308,6 +334,8 @@ def _mixer_times(cfg, device, timer: Timer, layer: int) -> Dict[str, float]:
     engine = _engine(cfg, device, DECODE_BATCH, DECODE_CONTEXT)
     _fill(engine)
     mixer = engine.model.blocks[layer].mixer
+    if pick is not None:
+        mixer = pick(engine.model.blocks[layer])
     memory = engine.memories[layer]
     width = engine.model.args.dim
     gen = torch.Generator().manual_seed(SEED)
@@ -323,7 +351,8 @@ def _mixer_times(cfg, device, timer: Timer, layer: int) -> Dict[str, float]:
     engine.admit("p")
     ctx = context([StepEntry("p", [1] * PREFILL_TOKENS, [])])
     x = torch.randn(PREFILL_TOKENS, width, generator=gen).to(device, torch.bfloat16)
-    out["prefill_us"] = round(timer.us(lambda: mixer.forward(x, ctx, memory)), 1)
+    run = (lambda x, ctx: mixer.forward(x, ctx, memory)) if hasattr(mixer, "cache_spec") else (lambda x, ctx: mixer.forward(x, ctx))
+    out["prefill_us"] = round(timer.us(lambda: run(x, ctx)), 1)
     engine.release("p")
     ids = [f"d{i}" for i in range(DECODE_BATCH)]
     for rid in ids:
@@ -332,7 +361,7 @@ def _mixer_times(cfg, device, timer: Timer, layer: int) -> Dict[str, float]:
         engine.cache.advance(r, DECODE_CONTEXT - 1)
     ctx = context([StepEntry(rid, [1], []) for rid in ids])
     x = torch.randn(DECODE_BATCH, width, generator=gen).to(device, torch.bfloat16)
-    out["decode_us"] = round(timer.us(lambda: mixer.forward(x, ctx, memory)), 1)
+    out["decode_us"] = round(timer.us(lambda: run(x, ctx)), 1)
     engine.ops.check_status()
     del engine
     torch.cuda.empty_cache()
@@ -475,9 +504,159 @@ def zeladra_kernel_table(size, device, peaks) -> Dict[str, dict]:
     return table
 
 
+def tanupel_kernel_table(size, device, peaks) -> Dict[str, dict]:
+    """The kernels of the Tanupel design alone at one size, each beside the like kernel of the
+    closest model where there is one (the Llama shape for norms, attention and the feed-forward;
+    Zeladra's state-space mixer for the recurrence): microseconds and the fraction of the roofline."""
+    from ..csrc.ops import Ops
+    from ..engine.step import StepContext
+
+    width, _layers, heads, kv, head_dim, ffn, vocab, window = size
+    ops = Ops(torch.bfloat16, device)
+    timer = Timer(device)
+    gen = torch.Generator().manual_seed(SEED)
+    hbm, tensor = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    table: Dict[str, dict] = {}
+
+    def bw(name, us, nbytes):
+        table[name] = dict(us=round(us, 1), gbs=round(nbytes / (us * 1e-6) / 1e9, 1), hbm_frac=round(nbytes / (us * 1e-6) / hbm, 3))
+
+    def rand(*shape, dtype=torch.bfloat16):
+        return torch.randn(*shape, generator=gen).to(device, dtype)
+
+    def context(t, n_seqs):
+        ctx = StepContext(device)
+        per = t // n_seqs
+        ctx.req = torch.arange(n_seqs, dtype=torch.int32, device=device).repeat_interleave(per)
+        ctx.seq_slot = torch.arange(n_seqs, dtype=torch.int32, device=device)
+        ctx.seq_start = torch.arange(0, t + 1, per, dtype=torch.int32, device=device)
+        ctx.n_tokens, ctx.n_seqs = t, n_seqs
+        return ctx
+
+    cfg = tanupel_config(*size)
+    right = cfg["layers"][0]["mixer"]["right"]
+    att = cfg["layers"][1]["mixer"]
+    for t in (PREFILL_TOKENS, DECODE_BATCH):
+        h = rand(t, width, dtype=torch.float32)
+        out = torch.empty(t, width, dtype=torch.bfloat16, device=device)
+        terms = [(rand(t, width), c) for c in (0.3, 0.55, 0.5)]
+        w32, row = rand(width, dtype=torch.float32), rand(width, dtype=torch.float32)
+        bw(f"norm+sum t={t}: one-plus rmsnorm of a sum (3 summands with factors, a row vector, sum, norm)",
+           timer.us(lambda: ops.rmsnorm_sum(h, terms, w32, 1e-5, out=out, row=row, one_plus=True)), t * width * (4 + 4 + 3 * 2 + 2))
+        delta, wb = rand(t, width), rand(width)
+        bw(f"norm+sum t={t}: rmsnorm (sum, norm; llama)", timer.us(lambda: ops.rmsnorm(h, wb, 1e-5, out=out, delta=delta)),
+           t * width * (4 + 4 + 2 + 2))
+        q, k = rand(t, att["heads"] * head_dim), rand(t, att["kv_heads"] * head_dim)
+        req = torch.zeros(t, dtype=torch.int32, device=device)
+        bw(f"query/key norm t={t}: mean squares over the whole projections",
+           timer.us(lambda: ops.qk_rstd(q, k, q.shape[1], k.shape[1], 1e-5, req)), t * (q.shape[1] + k.shape[1]) * 2)
+
+    # the gated delta rule's own kernels, beside the state-space mixer's of Zeladra at this size
+    H, G, d, dv, taps = right["heads"], right["kv_heads"], right["dim"], right["vdim"], right["conv"]
+    channels = 2 * G * d + H * dv
+    state = torch.zeros(DECODE_BATCH, H * dv * d + (taps - 1) * channels, dtype=torch.float32, device=device)
+    conv_w = rand(channels, taps, dtype=torch.float32)
+    dt_bias, a_log, norm_w = rand(H * d, dtype=torch.float32), rand(H, dtype=torch.float32), rand(dv, dtype=torch.float32)
+    for t, n_seqs in ((PREFILL_TOKENS, 1), (DECODE_BATCH, DECODE_BATCH)):
+        proj, a, b, z = rand(t, channels), rand(t, H * d), rand(t, H), rand(t, H * dv)
+        ctx = context(t, n_seqs)
+        bw(f"delta rule t={t}: convolution + SiLU", timer.us(lambda: ops.conv_silu(
+            proj, 0, channels, conv_w, state, H * dv * d, taps, ctx)), t * channels * (2 + 4))
+        qkv = ops.conv_silu(proj, 0, channels, conv_w, state, H * dv * d, taps, ctx)
+        state_bytes = n_seqs * H * dv * d * 8
+        bw(f"delta rule t={t}: recurrence ({n_seqs} sequences, {H} heads, state {d} x {dv})", timer.us(lambda: ops.delta_scan(
+            qkv, a, b, dt_bias, a_log, state, ctx, H, G, d, dv)), t * (channels * 4 + H * d * 2 + H * dv * 4) + state_bytes)
+        y = ops.delta_scan(qkv, a, b, dt_bias, a_log, state, ctx, H, G, d, dv)
+        bw(f"delta rule t={t}: norm per head + gate", timer.us(lambda: ops.head_norm_gate(y, z, norm_w, H, dv, 1e-5, ctx)),
+           t * H * dv * (4 + 2 + 2))
+        state.zero_()
+    ssm = zeladra_config(*size)["layers"][1]["mixer"]
+    sH, P, N, sG, staps = ssm["heads"] // 2, ssm["vdim"], ssm["state"], ssm["groups"], ssm["conv"]  # half the heads: a state of like size
+    inner, sch = sH * P, sH * P + 2 * sG * N
+    cols = 2 * inner + 2 * sG * N + sH
+    sstate = torch.zeros(DECODE_BATCH, sH * N * P + (staps - 1) * sch, dtype=torch.float32, device=device)
+    sconv_w, sconv_b = rand(sch, staps, dtype=torch.float32), rand(sch, dtype=torch.float32)
+    vec = [rand(sH, dtype=torch.float32) for _ in range(3)]
+    for t, n_seqs in ((PREFILL_TOKENS, 1), (DECODE_BATCH, DECODE_BATCH)):
+        proj = rand(t, cols)
+        ctx = context(t, n_seqs)
+        xbc = ops.mamba2_conv(proj, inner, sch, sconv_w, sconv_b, sstate, sH * N * P, staps, ctx)
+        bw(f"state-space (zeladra) t={t}: recurrence ({n_seqs} sequences, {sH} heads, state {N} x {P})", timer.us(lambda: ops.mamba2_scan(
+            xbc, proj, inner + sch, *vec, sstate, ctx, sH, sG, N, P)), t * (sch + inner) * 4 + n_seqs * sH * N * P * 8)
+        sstate.zero_()
+
+    # routed experts beside a dense gated feed-forward of as many parameters
+    mlp = cfg["layers"][2]["mlp"]
+    E, top, f = mlp["router"]["experts"], mlp["router"]["top"], mlp["expert"]["ff"]
+    w1, w3, w2 = rand(E, f, width), rand(E, f, width), rand(E, width, f)
+    router, corr = rand(E, width, dtype=torch.float32), 0.01 * rand(E, dtype=torch.float32)
+    w13, wd = rand(2 * ffn, width), rand(width, ffn)
+    for t in (PREFILL_TOKENS, DECODE_BATCH):
+        x = rand(t, width)
+        ctx = context(t, 1)
+        logits = ops.linear_f32(x, router)
+        ids, weights = ops.moe_route(logits, corr, top, ctx)
+        row = dict(router_logits_us=round(timer.us(lambda: ops.linear_f32(x, router)), 1),
+                   choice_us=round(timer.us(lambda: ops.moe_route(logits, corr, top, ctx)), 1))
+        us = timer.us(lambda: ops.moe_experts(x, ids, weights, w1, w3, w2))
+        row["experts_us"] = round(us, 1)
+        row["experts_tflops"] = round(6 * t * top * f * width / (us * 1e-6) / 1e12, 1)
+        row["experts_tensor_frac"] = round(6 * t * top * f * width / (us * 1e-6) / tensor, 3)
+        touched = min(E, t * top)
+        row["experts_weight_gbs"] = round(touched * 3 * f * width * 2 / (us * 1e-6) / 1e9, 1)
+        row["experts_hbm_frac"] = round(touched * 3 * f * width * 2 / (us * 1e-6) / hbm, 3)
+        table[f"routed experts t={t}: {top} of {E} experts of {f} rows"] = row
+
+        def dense():
+            g = ops.linear_swiglu(x, w13)
+            if g is None:
+                g = torch.empty(t, ffn, dtype=torch.bfloat16, device=device)
+                ops.silu_gate(ops.linear(x, w13), g)
+            return ops.linear(g, wd)
+        us = timer.us(dense)
+        table[f"dense gated feed-forward t={t}: {ffn} rows (llama)"] = dict(
+            us=round(us, 1), tflops=round(6 * t * ffn * width / (us * 1e-6) / 1e12, 1),
+            tensor_frac=round(6 * t * ffn * width / (us * 1e-6) / tensor, 3),
+            weight_gbs=round(3 * ffn * width * 2 / (us * 1e-6) / 1e9, 1), hbm_frac=round(3 * ffn * width * 2 / (us * 1e-6) / hbm, 3))
+
+    small = (width, 2, heads, kv, head_dim, ffn, 1024)
+    tz = tanupel_config(*small)
+    left = tz["layers"][0]["mixer"]["left"]
+    table["attention softmax, capped scores (tanupel pair's left half, causal)"] = _attention_times(
+        tz, device, timer, 0, None, left["heads"], left["kv_heads"], head_dim, pick=lambda m: m.left)
+    table["attention softmax (tanupel 'attention', causal)"] = _attention_times(tz, device, timer, 1, None, heads, kv, head_dim)
+    table["attention softmax (llama, causal)"] = _attention_times(llama_config(*small), device, timer, 0, None, heads, kv, head_dim)
+    for name, row in table.items():
+        if "prefill_tflops" in row:
+            row["prefill_tensor_frac"] = round(row["prefill_tflops"] * 1e12 / tensor, 3)
+            row["decode_hbm_frac"] = round(row["decode_gbs"] * 1e9 / hbm, 3)
+    # whole mixers (projections included) and whole feed-forwards
+    table["mixer pair (tanupel: capped attention beside the delta rule; whole mixer)"] = _mixer_times(tz, device, timer, 0)
+    table["mixer pair's right half alone (tanupel delta rule; whole mixer)"] = _mixer_times(tz, device, timer, 0, pick=lambda b: b.mixer.right)
+    table["mixer attention (tanupel, projection-wide query/key norm; whole mixer)"] = _mixer_times(tz, device, timer, 1)
+    table["mixer attention (llama, causal; whole mixer)"] = _mixer_times(llama_config(*small), device, timer, 0)
+    return table
+
+
 def run(sizes: List[str], peaks: dict, kernels: bool = True, design: str = "sinorax") -> dict:
     device = torch.device("cuda:0")
     torch.cuda.set_device(device)
+    if design == "tanupel":
+        out = {"metric": "prefill and decode tokens/s of Tanupel beside a Llama-shaped model of equal size (bf16, random weights)",
+               "unit": "tokens/s", "dtype": "bf16", "data": "synthetic (random weights, uniform random token ids)",
+               "config": dict(prefill_tokens=PREFILL_TOKENS, decode_batch=DECODE_BATCH, decode_context=DECODE_CONTEXT, page=PAGE,
+                              l2="flushed before every timed kernel; model steps stream all weights"),
+               "peaks": peaks, "sizes": {}}
+        for name in sizes:
+            size = SIZES[name]
+            entry = dict(width=size[0], layers=size[1], heads=size[2], kv_heads=size[3], head_dim=size[4], swiglu_ffn=size[5],
+                         vocab=size[6], experts=8, top=2, expert_ffn=size[5] // 8)
+            entry["tanupel"] = model_throughput(tanupel_config(*size), device)
+            entry["llama"] = model_throughput(llama_config(*size[:7]), device)
+            if kernels:
+                entry["kernels"] = tanupel_kernel_table(size, device, peaks)
+            out["sizes"][name] = entry
+        return out
     if design == "zeladra":
         out = {"metric": "prefill and decode tokens/s of Zeladra beside a Llama-shaped model of equal size (bf16, random weights)",
                "unit": "tokens/s", "dtype": "bf16", "data": "synthetic (random weights, uniform random token ids)",

@@ -72,12 +72,13 @@ TA = dict(
     ],
 )
 # no repeated run, no embedding scale, a multiplier of one; one expert of one; a convolution of one
-# tap (no inputs to keep); a delta rule of one head with a state of one column; heads that rotate whole
+# tap (no inputs to keep); a delta rule of one head (a state of one column is in the rule's own test:
+# its norm is a sign, which no rounding survives); heads that rotate whole
 TB = dict(
     architecture="Tanupel", vocab=97, width=64, norm=dict(eps=1e-6),
     layers=[
         _layer("parallel", _pair(_attn(2, 2, 16, 16, 0.25, dims=16, base=777.0, scaling=(1.5,), softcap=50.0),
-                                 _delta(1, 1, 33, 1, 1, 3, 1), 1.0, 1.0), _moe(1, 1, 56)),
+                                 _delta(1, 1, 33, 5, 1, 3, 1), 1.0, 1.0), _moe(1, 1, 56)),
         _layer("attention", _attn(4, 1, 16, 8, 0.25, dims=16, base=1e4, scaling=(4.0, 1.0, 2.0, 16)), _dense(100)),
         _layer("parallel", _pair(_attn(1, 1, 64, 64, 0.1, dims=2, base=50.0, scaling=(3.0,), softcap=1.0),
                                  _delta(6, 3, 8, 24, 8, 2, 2), 0.3, 2.0), None),
@@ -495,3 +496,384 @@ def test_decay_acts_per_head_and_key_channel(dtype):
     out, _ = _run_mixer(mixer, cache, x, (17, 1, 1, 21), dtype)
     ops.check_status()
     _close(out, ref, dtype)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("sizes", [
+    # heads, key/value heads, key size, value size, scale, turned dimensions, base, scaling, cap, divide
+    (6, 3, 16, 32, 0.2, 8, 5000.0, (8.0, 1.0, 4.0, 64), None, False),
+    (4, 2, 32, 16, 0.15, 32, 1e4, (2.0,), 5.0, True),
+    (4, 2, 32, 16, 0.15, 16, 1e4, (2.0, 1.0, 4.0, 64), 5.0, True),   # a pair's attention divides all the same
+    (2, 1, 48, 48, 0.12, 24, 300.0, None, None, False),
+    (1, 1, 64, 64, 0.1, 2, 50.0, (3.0,), 1.0, True),
+    (5, 1, 16, 32, 0.2, 16, 1e4, (2.0,), 8.0, True),
+    (2, 2, 80, 16, 0.11, 40, 2000.0, (2.0, 1.0, 8.0, 32), None, False),
+    (3, 3, 24, 24, 0.3, None, 1.0, None, 2.0, False),                # no positions at all
+])
+def test_attention_alone(dtype, sizes):
+    """Queries and keys normed over the whole projection, a part of each head turned (dimension i
+    with dimension i + half), frequencies bent by wavelength, divided or left, scores capped or
+    not, value heads larger and smaller than key heads: a portion, single tokens and short
+    portions across pages of eight; then the pages are freed and taken again."""
+    from fastgen_b200.config.tanupel import _attention
+    from fastgen_b200.cache import CacheManager
+    from fastgen_b200.parts import make_mixer
+
+    heads, kv, d, dv, scale, dims, base, scaling, cap, divide = sizes
+    g = torch.Generator().manual_seed(heads * 100 + d)
+    m = _attn(heads, kv, d, dv, scale, dims=dims, base=base, scaling=scaling, softcap=cap)
+    ops = _ops(dtype)
+    mixer = make_mixer(_attention(40, 1e-5, m, "mix.", "test", by_wavelength=not divide))
+    w = _draw_all(mixer, g, 0.3, None)
+    mixer.bind({local: w[name].to(DEV) for local, name in mixer.names.items()}, ops)
+    cache = CacheManager([mixer.cache_spec()], [mixer.state_spec()], [None], 8, 16, 2, 128, dtype=dtype, device=DEV,
+                         tensor_map_factory=ops.make_kv_tensor_maps)
+    w = {k: v.double() for k, v in w.items()}
+    x = torch.randn(75, 40, generator=g).to(dtype)
+    ref = pt.softmax_attention(x.double(), m, w, "mix.", 1e-5, linear_scaling=divide)
+    if scaling and len(scaling) == 4:
+        alt = pt.softmax_attention(x.double(), m, w, "mix.", 1e-5, linear_scaling=not divide)
+        assert float((alt - ref).abs().max()) > 0.02 * float(ref.abs().max())
+    out, req = _run_mixer(mixer, cache, x, (33, 1, 1, 7, 1, 2, 3, 1, 26), dtype)
+    ops.check_status()
+    _close(out, ref, dtype)
+    cache.release("r")
+    out2, _ = _run_mixer(mixer, cache, x[:30], (2, 1, 27), dtype, rid="again")
+    _close(out2, ref[:30], dtype, float(ref.abs().max()))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("mode", ["prompt", "decoded"])
+def test_far_key_shows_through_the_cap(dtype, mode):
+    """One key 400 positions back has a score far above all others, through a dimension that is not
+    turned.  Capped, it takes about half of the weight; uncapped it would take all of it, and
+    without the key the output is another one: in a prompt portion and for tokens decoded alone,
+    with the key on the first of many pages."""
+    from fastgen_b200.config.tanupel import _attention
+
+    heads, kv, d, n, cap = 2, 1, 16, 420, 6.0
+    g = torch.Generator().manual_seed(21)
+    m = _attn(heads, kv, d, d, 3.0, dims=8, base=1e4, scaling=(2.0,), softcap=cap)
+
+    def tweak(w):
+        for h in range(heads):
+            w["mix.q"][h * d + d - 1, :] = 0
+            w["mix.q"][h * d + d - 1, 0] = 4.0
+        w["mix.k"][d - 1, :] = 0
+        w["mix.k"][d - 1, 1] = 4.0
+        w["mix.q.norm"][:] = 1.0
+        w["mix.k.norm"][:] = 1.0
+    mixer, cache, w, ops = _mixer_and_cache("attention", m, 24, dtype, g, page=16, n_pages=32, std=0.05, tweak=tweak)
+    x = 0.3 * torch.randn(n, 24, generator=g)
+    x[:, :2] = 0.0
+    far, q1, q2 = 3, n - 1, n - 40
+    x[far, 1] = 3.0
+    x[q1, 0] = x[q2, 0] = 3.0
+    x = x.to(dtype)
+    ref = pt.softmax_attention(x.double(), m, w, "mix.", 1e-5, False)
+    x0 = x.clone()
+    x0[far] = 0
+    without = pt.softmax_attention(x0.double(), m, w, "mix.", 1e-5, False)
+    uncapped = pt.softmax_attention(x.double(), dict(m, softcap=None), w, "mix.", 1e-5, False)
+    for q in (q1, q2):
+        scale = float(ref[q].abs().max())
+        assert float((ref[q] - without[q]).abs().max()) > 0.15 * scale
+        assert float((ref[q] - uncapped[q]).abs().max()) > 0.15 * scale
+    out, _ = _run_mixer(mixer, cache, x, (300, 120) if mode == "prompt" else (300, 70) + (1,) * 50, dtype)
+    ops.check_status()
+    for q in (q1, q2):
+        assert float((out[q] - ref[q]).abs().max()) <= _tol(dtype) * float(ref[q].abs().max()), q
+    _close(out, ref, dtype)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_keys_at_page_borders(dtype):
+    """The only keys that matter sit on the last place of a page and the first of the next; the
+    queries come as portions that end and start there, and as single tokens."""
+    g = torch.Generator().manual_seed(23)
+    d = 16
+    m = _attn(2, 2, d, d, 2.5, dims=4, base=100.0)
+
+    def tweak(w):
+        for h in range(2):
+            for t in ("mix.q", "mix.k"):
+                w[t][h * d + d - 1, :] = 0
+                w[t][h * d + d - 1, 0] = 4.0
+        w["mix.q.norm"][:] = 1.0
+        w["mix.k.norm"][:] = 1.0
+    mixer, cache, w, ops = _mixer_and_cache("attention", m, 24, dtype, g, page=8, n_pages=16, std=0.05, tweak=tweak)
+    x = 0.3 * torch.randn(64, 24, generator=g)
+    x[:, 0] = 0.0
+    for i in (7, 8, 31, 32, 40, 47, 48, 63):
+        x[i, 0] = 3.0
+    x = x.to(dtype)
+    ref = pt.softmax_attention(x.double(), m, w, "mix.", 1e-5, False)
+    for portions in ((8, 24, 8, 7, 1, 16), (7, 1, 1, 23) + (1,) * 32, (64,)):
+        out, _ = _run_mixer(mixer, cache, x, portions, dtype)
+        ops.check_status()
+        _close(out, ref, dtype)
+        cache.release("r")
+
+
+def _feed_forward_alone(mlp, dim, dtype, g, std=0.3, tweak=None):
+    from fastgen_b200.config.tanupel import _feed_forward
+    from fastgen_b200.parts import make_feed_forward
+
+    ops = _ops(dtype)
+    ff = make_feed_forward(_feed_forward(dim, mlp, "mlp.", "test"))
+    w = _draw_all(ff, g, std, tweak)
+    ff.bind({local: w[name].to(DEV) for local, name in ff.names.items()}, ops)
+    return ff, {k: v.double() for k, v in w.items()}, ops
+
+
+def _clear_choices(x, mlp, w, margin):
+    """Tokens whose last chosen expert leads the best one left out by more than ``margin``."""
+    s = torch.softmax(x @ w["mlp.router"].T, dim=-1)
+    c = torch.sort(s + w["mlp.correction"], dim=-1, descending=True).values
+    top = mlp["router"]["top"]
+    if top == c.shape[1]:
+        return torch.ones(x.shape[0], dtype=torch.bool)
+    return (c[:, top - 1] - c[:, top]) > margin
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("sizes", [(5, 3, 40), (7, 1, 24), (1, 1, 56), (3, 3, 32), (12, 2, 96), (9, 4, 8), (33, 5, 16),
+                                   (64, 8, 24)])
+@pytest.mark.parametrize("tokens", [1, 3, 70])
+def test_routed_experts_alone(dtype, sizes, tokens):
+    """Softmax over all experts in float32, the choice by score plus correction, the weights by
+    the score alone and not renormalized; one expert, all experts, more experts than a warp has
+    lanes; one token, a few, and more tokens than experts."""
+    experts, top, ff = sizes
+    g = torch.Generator().manual_seed(experts * 10 + top)
+    mlp = _moe(experts, top, ff)
+    part, w, ops = _feed_forward_alone(mlp, 48, dtype, g)
+    x = torch.randn(tokens, 48, generator=g).to(dtype)
+    ref = pt.routed_experts(x.double(), mlp, w, "mlp.")
+    out = _value(part.forward(x.to(DEV), _context(0, 0, tokens))).cpu()
+    ops.check_status()
+    ok = _clear_choices(x.double(), mlp, w, 1e-5)  # both see the same rounded input: float32 sums are that close
+    assert int(ok.sum()) >= (tokens * 2 + 2) // 3
+    _close(out[ok], ref[ok], dtype, float(ref.abs().max()))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_the_correction_chooses_and_does_not_weigh(dtype):
+    """A correction that lifts the expert with the smallest score into the choice: the output is
+    that expert's, weighted by its small score; adding the correction to the weight, dividing by
+    the chosen scores' sum, or choosing by the score alone would each give another output."""
+    g = torch.Generator().manual_seed(31)
+    experts, top = 6, 2
+    mlp = _moe(experts, top, 32)
+
+    def tweak(w):
+        w["mlp.router"] = (0.2 * torch.randn(experts, 48, generator=g)).bfloat16()
+        w["mlp.router"][4] = -w["mlp.router"][0]      # expert 4 scores low where expert 0 scores high
+        corr = torch.zeros(experts)
+        corr[4] = 5.0
+        w["mlp.correction"] = corr.bfloat16()
+    part, w, ops = _feed_forward_alone(mlp, 48, dtype, g, tweak=tweak)
+    x = torch.randn(40, 48, generator=g).to(dtype)
+    xd = x.double()
+    ref = pt.routed_experts(xd, mlp, w, "mlp.")
+    s = torch.softmax(xd @ w["mlp.router"].T, dim=-1)
+    choice = torch.topk(s + w["mlp.correction"], top, dim=-1).indices
+    assert bool((choice == 4).any(dim=-1).all())
+
+    def expert(e, rows):
+        a = rows @ w[f"mlp.e{e}.gate"].T
+        return (pt.silu(a) * (rows @ w[f"mlp.e{e}.up"].T)) @ w[f"mlp.e{e}.down"].T
+    others = []
+    for how in ("corrected weight", "renormalized", "score alone"):
+        alt = torch.zeros_like(ref)
+        for t in range(40):
+            ids = torch.topk(s[t], top).indices if how == "score alone" else choice[t]
+            wts = s[t, ids]
+            if how == "corrected weight":
+                wts = wts + w["mlp.correction"][ids]
+            if how == "renormalized":
+                wts = wts / wts.sum()
+            alt[t] = sum(wt * expert(int(e), xd[t:t + 1])[0] for e, wt in zip(ids, wts))
+        others.append(alt)
+        assert float((alt - ref).abs().max()) > 0.2 * float(ref.abs().max()), how
+    out = _value(part.forward(x.to(DEV), _context(0, 0, 40))).cpu()
+    ops.check_status()
+    ok = _clear_choices(xd, mlp, w, 1e-5)
+    _close(out[ok], ref[ok], dtype, float(ref.abs().max()))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_two_mixers_side_by_side(dtype):
+    """Both halves read the same input; the sum takes each half with its own scale; the attention
+    of the pair has the pages, the delta rule the slot's state."""
+    g = torch.Generator().manual_seed(41)
+    m = _pair(_attn(4, 2, 32, 16, 0.15, dims=16, base=1e4, scaling=(2.0, 1.0, 4.0, 64), softcap=5.0),
+              _delta(4, 2, 24, 40, 3, 8, 12), 0.7, 1.3)
+    mixer, cache, w, ops = _mixer_and_cache("parallel", m, 56, dtype, g, std=0.25)
+    x = torch.randn(50, 56, generator=g).to(dtype)
+    ref = pt.two_mixers(x.double(), m, w, "mix.", 1e-5)
+    left = pt.softmax_attention(x.double(), m["left"], w, "mix.left.", 1e-5, True)
+    right = pt.gated_delta_rule(x.double(), m["right"], w, "mix.right.", 1e-5)
+    assert float((ref - (0.7 * left + 1.3 * right)).abs().max()) < 1e-9
+    assert float((ref - (left + right)).abs().max()) > 0.05 * float(ref.abs().max())
+    out, _ = _run_mixer(mixer, cache, x, (20, 1, 1, 2, 5, 1, 20), dtype)
+    ops.check_status()
+    _close(out, ref, dtype)
+
+
+# ---------------------------------------------------------------------------------
+# whole models through the engine
+# ---------------------------------------------------------------------------------
+def model_dir(tmp_path, name, dtype):
+    """The model folder of a configuration.  In bfloat16 the engine's activations differ from the
+    plain implementation's by a percent, which turns a token's choice of experts wherever two
+    choice scores are that close, so the folder of the bfloat16 runs gets corrections two apart
+    (scores lie between 0 and 1): there every token takes the same experts, with weights of its
+    own.  Choices that depend on the token are held in float32, and in bfloat16 by
+    ``test_routed_experts_alone``."""
+    from safetensors.torch import load_file, save_file
+
+    if dtype == torch.float32:
+        return make_dir(tmp_path, name)
+    d = make_dir(Path(tmp_path) / "apart", name)
+    f = Path(d) / "model.safetensors"
+    tensors = load_file(str(f))
+    g = torch.Generator().manual_seed(CONFIGS[name][1])
+    for key in [k for k in tensors if k.endswith(".correction")]:
+        n = tensors[key].numel()
+        tensors[key] = (2.0 * torch.randperm(n, generator=g)).to(tensors[key].dtype)
+    save_file(tensors, str(f))
+    return d
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("name", ["ta", "tb", "tc", "td"])
+@pytest.mark.parametrize("plan", ["whole", "decode", "portions", "mixed"])
+def test_replay(tmp_path, name, dtype, plan):
+    """Whole prompts (of one and two tokens too), prompts with a decoded tail, portions of 2 to 17
+    tokens, and mixed batches of up to four requests whose pages and slots are used again, all
+    against the plain implementation run on whole sequences."""
+    d = model_dir(tmp_path, name, dtype)
+    vocab = CONFIGS[name][0]["vocab"]
+    page = 16
+    if plan == "mixed":
+        requests = _requests(vocab, [70, 33, 1, 90, 18, 64, 47, 2], 40)
+        steps = H.plan_mixed(requests, seed=5)
+    else:
+        requests = _requests(vocab, [1, 2, 37, 150] if plan != "portions" else [2, 95], 20)
+        steps = {"whole": H.plan_whole, "decode": lambda r: H.plan_decode_tail(r, 45), "portions": H.plan_portions}[plan](requests)
+    outputs, engine = H.run_engine(d, dtype, steps, page, H.max_live_tokens(steps, page) + 2 * page)
+    compare(d, requests, H.collect(steps, outputs), dtype)
+    assert engine.cache.n_live == 0 and all(f == g.pool.n_pages for f, g in zip(engine.cache.free_pages(), engine.cache.groups))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("name", ["ta", "tc"])
+def test_batching_changes_nothing(tmp_path, dtype, name):
+    """A request's logits in a batch of unequal requests equal those it gets alone (bitwise in
+    float32, where every sum has a fixed order; within rounding in bfloat16)."""
+    d = model_dir(tmp_path, name, dtype)
+    requests = _requests(CONFIGS[name][0]["vocab"], [41, 5, 77, 20], 60)
+    alone = H.plan_portions(requests, sizes=(9, 1, 1, 30))
+    out_a, _ = H.run_engine(d, dtype, alone, 8, H.max_live_tokens(alone, 8) + 32)
+    got_a = H.collect(alone, out_a)
+    mixed = H.plan_mixed(requests, seed=2)
+    out_m, _ = H.run_engine(d, dtype, mixed, 8, H.max_live_tokens(mixed, 8) + 32)
+    got_m = H.collect(mixed, out_m)
+    for rid, toks in requests.items():
+        for p in range(len(toks)):
+            if dtype == torch.float32:
+                assert np.array_equal(got_a[rid][p], got_m[rid][p]), (rid, p)
+            else:
+                check_row(got_m[rid][p], got_a[rid][p], dtype, f"{rid} {p}")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("name", ["ta", "tc"])
+def test_steps_replayed_from_graphs_change_nothing(tmp_path, dtype, name):
+    """Steps captured as CUDA graphs (single tokens, and prompt portions padded to a few shapes)
+    give what the same steps give launched kernel by kernel: states and convolution inputs are
+    advanced by the replays only, never by a capture, and padding lanes choose no expert."""
+    d = model_dir(tmp_path, name, dtype)
+    requests = _requests(CONFIGS[name][0]["vocab"], [41, 5, 77, 20], 61)
+    mixed = H.plan_mixed(requests, seed=3)
+    room = H.max_live_tokens(mixed, 8) + 32
+    out_g, eng = H.run_engine(d, dtype, mixed, 8, room, max_step_tokens=64)
+    assert eng.graphs is not None and eng.step_graphs is not None and eng.step_graphs.replays > 0
+    out_p, _ = H.run_engine(d, dtype, mixed, 8, room, num_cuda_graphs=0)
+    got_g, got_p = H.collect(mixed, out_g), H.collect(mixed, out_p)
+    for rid, toks in requests.items():
+        for p in range(len(toks)):
+            if dtype == torch.float32:
+                assert np.array_equal(got_g[rid][p], got_p[rid][p]), (rid, p)
+            else:
+                check_row(got_g[rid][p], got_p[rid][p], dtype, f"{rid} {p}")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_long_decoding(tmp_path, dtype):
+    """200 tokens decoded one by one after a two-token prompt, over many pages of eight: every
+    pass's cache grows by itself and every pass's state is carried."""
+    d = model_dir(tmp_path, "ta", dtype)
+    requests = _requests(211, [202], 77)
+    steps = H.plan_decode_tail(requests, 200)
+    outputs, engine = H.run_engine(d, dtype, steps, 8, 232)
+    compare(d, requests, H.collect(steps, outputs), dtype)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("name", ["ta", "td"])
+def test_slots_used_again_start_from_zero(tmp_path, dtype, name):
+    """Two slots only: six requests pass through them one after the other, some ending in the
+    middle of a step of the others; a state or a convolution input left by a slot's earlier
+    request would show in the first tokens of the next."""
+    d = model_dir(tmp_path, name, dtype)
+    requests = _requests(CONFIGS[name][0]["vocab"], [30, 9, 41, 3, 26, 12], 81)
+    steps = H.plan_mixed(requests, seed=7, max_live=2)
+    outputs, engine = H.run_engine(d, dtype, steps, 8, H.max_live_tokens(steps, 8) + 16, max_requests=2)
+    compare(d, requests, H.collect(steps, outputs), dtype)
+    assert engine.cache.n_live == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("name", ["ta", "tc"])
+def test_greedy_generation_through_the_entry_point(tmp_path, dtype, name):
+    """``Fastgen.generate`` with its scheduler (portions of 16 tokens, batches of 3, graphs)
+    against greedy decoding with the plain implementation."""
+    from fastgen_b200.engine import Fastgen, GenArgs, HfLoader, Packet
+
+    d = model_dir(tmp_path, name, dtype)
+    cfg, w = pt.read_model(d)
+    vocab = cfg["vocab"]
+    prompts = [H.random_tokens(vocab, n, 90 + n) for n in (7, 1, 40, 23)]
+    fg = Fastgen.build(HfLoader(d), GenArgs(use_sampling=False, max_gen=12, cache_block=16, max_seq=128, max_batch=3,
+                                            max_prefill=16),
+                       tp_mesh=None, device=torch.device(DEV), dtype=dtype)
+    q = queue.Queue()
+    for i, p in enumerate(prompts):
+        q.put(Packet(thread_id=i, tokens=p))
+    q.put(None)
+    got = {pkt.thread_id: pkt.tokens for pkt in fg.generate(q)}
+    fg.destroy()
+    for i, p in enumerate(prompts):
+        assert len(got[i]) == 12
+        if dtype == torch.float32:
+            assert got[i] == pt.greedy(cfg, w, p, 12), i
+        else:
+            seq = list(p)
+            for tok in got[i]:
+                logits = pt.forward(cfg, w, seq)[-1]
+                assert float(logits[tok]) >= float(logits.max()) - 0.03 * float(logits.abs().max())
+                seq.append(tok)
