@@ -507,7 +507,7 @@ extern "C" int fg_attention_prefill_tc5_bf16(const void* q, int q_stride, void* 
                                              int n_heads, int n_kv_heads, int head_dim, int window, float scale,
                                              unsigned int* work_counter, float* split_scratch, int* split_flags,
                                              int split_slots, int max_keys, const int* real_tiles, int nominal_tiles,
-                                             int* status, cudaStream_t stream) {
+                                             float softcap, int* status, cudaStream_t stream) {
   if (n_tiles == 0) return 0;
   FG_CHECK_ARG(work_counter != nullptr, "fg_attention_prefill_tc5_bf16: no work counter");
   FG_CHECK_ARG(head_dim == FG_HEAD_DIM, "fg_attention_prefill_tc5_bf16: library built for head size %d, got %d",
@@ -524,14 +524,17 @@ extern "C" int fg_attention_prefill_tc5_bf16(const void* q, int q_stride, void* 
   memcpy(&km, k_map, sizeof(CUtensorMap));
   memcpy(&vm, v_map, sizeof(CUtensorMap));
   constexpr size_t smem = fg_tc5::smem_bytes<FG_HEAD_DIM>();
-  auto kern_whole = fg_tc5::attention_prefill_tc5_kernel<FG_HEAD_DIM, false>;
-  auto kern_parts = fg_tc5::attention_prefill_tc5_kernel<FG_HEAD_DIM, true>;
-  static bool attr_set = false;
-  if (!attr_set) {
+  const bool capped = softcap > 0.f;
+  auto kern_whole = capped ? fg_tc5::attention_prefill_tc5_kernel<FG_HEAD_DIM, false, false, true>
+                           : fg_tc5::attention_prefill_tc5_kernel<FG_HEAD_DIM, false>;
+  auto kern_parts = capped ? fg_tc5::attention_prefill_tc5_kernel<FG_HEAD_DIM, true, false, true>
+                           : fg_tc5::attention_prefill_tc5_kernel<FG_HEAD_DIM, true>;
+  static bool attr_set[2] = {false, false};
+  if (!attr_set[capped]) {
     cudaError_t e = cudaFuncSetAttribute(kern_whole, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(kern_parts, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     FG_CHECK_ARG(e == cudaSuccess, "fg_attention_prefill_tc5_bf16: shared memory: %s", cudaGetErrorString(e));
-    attr_set = true;
+    attr_set[capped] = true;
   }
   // two blocks an SM take the (tile, kv head, slice of the group) items from a counter
   const long long items = tc5_items(n_tiles, n_heads, n_kv_heads);
@@ -547,8 +550,8 @@ extern "C" int fg_attention_prefill_tc5_bf16(const void* q, int q_stride, void* 
   (split ? kern_parts : kern_whole)<<<grid, fg_tc5::THREADS, smem, stream>>>(
       km, vm, layer, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, block_table, table_width,
       page_size, n_pages, pos, tile_req, tile_tok0, tile_ntok, n_tiles, n_kv_heads, group, hpb, window,
-      scale * 1.4426950408889634f, work_counter, parts, split_scratch, split_flags, split_slots, real_tiles, status,
-      nullptr, nullptr, nullptr);
+      (capped ? softcap : scale) * 1.4426950408889634f, work_counter, parts, split_scratch, split_flags, split_slots,
+      real_tiles, status, nullptr, nullptr, nullptr, capped ? scale / softcap : 0.f);
   FG_CHECK_LAUNCH("fg_attention_prefill_tc5_bf16");
   return 0;
 }
@@ -597,7 +600,7 @@ extern "C" int fg_attention_sigmoid_prefill_tc5_bf16(const void* q, int q_stride
   kern<<<grid, fg_tc5::THREADS, smem, stream>>>(
       km, vm, layer, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, block_table, table_width,
       page_size, n_pages, pos, tile_req, tile_tok0, tile_ntok, n_tiles, n_kv_heads, group, hpb, window,
-      scale * 1.4426950408889634f, work_counter, 1, nullptr, nullptr, 0, real_tiles, status, gate, r1, r2);
+      scale * 1.4426950408889634f, work_counter, 1, nullptr, nullptr, 0, real_tiles, status, gate, r1, r2, 0.f);
   FG_CHECK_LAUNCH("fg_attention_sigmoid_prefill_tc5_bf16");
   return 0;
 }

@@ -190,7 +190,12 @@ __device__ __noinline__ void merge_parts(const float* slots, int n_parts, __nv_b
 // over the keys: the softmax warps compute the weights in base 2 on the special-function unit
 // (lg2, ex2, rcp), keep no maximum and no sum, never rescale O and store it as it is.  Such a
 // launch does not split its items.
-template <int HD, bool SPLIT, bool SIGMOID = false>
+//
+// CAPPED: a score s enters the softmax as cap * tanh(s * scale / cap).  The launch passes
+// `cap_in` = scale / cap and `scale_log2` = cap * log2(e): the softmax warps turn every score
+// into tanh(s * cap_in) as they read it (1 - 2 / (1 + 2^(2 x log2 e)) on the special-function
+// unit: exact to a few 1e-7 over the whole range, and -1 and 1 at its ends) and go on in base 2.
+template <int HD, bool SPLIT, bool SIGMOID = false, bool CAPPED = false>
 __global__ void __launch_bounds__(THREADS, 2)
 attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                              int layer, const __nv_bfloat16* __restrict__ q, int q_stride,
@@ -201,8 +206,10 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
                              int heads_per_block, int window, float scale_log2, unsigned int* work_counter,
                              int parts, float* split_scratch, int* split_flags, int split_slots,
                              const int* real_tiles, int* status, const float* __restrict__ gate,
-                             const float* __restrict__ dist_r1, const float* __restrict__ dist_r2) {
+                             const float* __restrict__ dist_r1, const float* __restrict__ dist_r2,
+                             float cap_in) {
   static_assert(HD == 64 || HD == 128, "head sizes 64 and 128");
+  static_assert(!(CAPPED && SIGMOID), "the cap belongs to the softmax");
   static_assert(!(SPLIT && SIGMOID), "launches with sigmoid weights do not split their items");
   constexpr int HALVES = HD / 64;
   constexpr int STAGE_BYTES = HALVES * KV_HALF;
@@ -515,6 +522,11 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
           const int k0 = k_lo + t * KEYS;
           float s[KEYS];
           tmem_ld64(s_addr, s);
+          if (CAPPED) {
+            const float two_l2e = 2.f * 1.4426950408889634f * cap_in;
+#pragma unroll
+            for (int i = 0; i < KEYS; ++i) s[i] = fmaf(-2.f, rcp_approx(1.f + ex2_approx(s[i] * two_l2e)), 1.f);
+          }
           const bool need_mask =
               !warp_full || k0 + KEYS - 1 > warp_min || (window > 0 && k0 <= warp_max - window);
           float alpha = 1.f;

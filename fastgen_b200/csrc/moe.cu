@@ -1,6 +1,7 @@
 // Feed-forward with routed experts: every token goes through `top` of `n_experts` small gated
 // feed-forwards and their outputs are summed with the router's weights.
 //
+//   fg_moe_logits  the router's logits x W^T in float32 (W float32, x of either type): a warp a token.
 //   fg_moe_route   scores s = softmax(logits) (float32); the experts with the largest s + correction
 //                  are chosen; their weights are their s, as they are (or divided by their sum).
 //   fg_moe_plan    sorts the (token, choice) pairs by expert (stable: ascending pair index within an
@@ -14,6 +15,53 @@
 //   fg_moe_gemm_mma the same product in bfloat16 on the tensor cores.
 //   fg_moe_combine ff[t, :] = sum_k weight[t, k] * y[row of (t, k), :], ascending k.
 #include "common.cuh"
+
+// ---- the router's logits ---------------------------------------------------------------------
+// logits[t, e] = sum_k x[t, k] w[e, k] in float32: a warp a token, eight experts at a time; lane l sums
+// k = l, l + 32, ... in ascending order and the lanes' sums meet in a fixed exchange tree, so a
+// token's logits do not depend on the batch around it.
+constexpr int LOGITS_GROUP = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_logits_kernel(const T* x, long ldx, const float* __restrict__ w, long ldw, float* __restrict__ logits,
+                  const int* __restrict__ req, int n_tokens, int n_experts, int K) {
+  const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (t >= n_tokens || (req != nullptr && req[t] < 0)) return;
+  const T* row = x + (size_t)t * ldx;
+  for (int e0 = 0; e0 < n_experts; e0 += LOGITS_GROUP) {
+    float acc[LOGITS_GROUP];
+#pragma unroll
+    for (int j = 0; j < LOGITS_GROUP; ++j) acc[j] = 0.f;
+    for (int k = lane; k < K; k += 32) {
+      const float xv = to_f32<T>(row[k]);
+#pragma unroll
+      for (int j = 0; j < LOGITS_GROUP; ++j)
+        if (e0 + j < n_experts) acc[j] = fmaf(xv, w[(size_t)(e0 + j) * ldw + k], acc[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < LOGITS_GROUP; ++j) {
+      const float total = warp_sum(acc[j]);
+      if (lane == 0 && e0 + j < n_experts) logits[(size_t)t * n_experts + e0 + j] = total;
+    }
+  }
+}
+
+extern "C" int fg_moe_logits(const void* x, int dtype, long ldx, const float* w, long ldw, float* logits,
+                             const int* req, int n_tokens, int n_experts, int K, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  FG_CHECK_ARG(n_experts >= 1 && K >= 1, "fg_moe_logits: %d experts over %d inputs", n_experts, K);
+  const int blocks = (n_tokens + 3) / 4;
+  if (dtype == FG_F32)
+    moe_logits_kernel<float><<<blocks, 128, 0, stream>>>((const float*)x, ldx, w, ldw, logits, req, n_tokens, n_experts, K);
+  else if (dtype == FG_BF16)
+    moe_logits_kernel<__nv_bfloat16><<<blocks, 128, 0, stream>>>((const __nv_bfloat16*)x, ldx, w, ldw, logits, req,
+                                                                 n_tokens, n_experts, K);
+  else
+    FG_CHECK_ARG(false, "fg_moe_logits: bad dtype %d", dtype);
+  FG_CHECK_LAUNCH("fg_moe_logits");
+  return 0;
+}
 
 constexpr int ROUTE_MAX_PER_LANE = 8;  // up to 256 experts
 

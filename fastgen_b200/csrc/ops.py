@@ -92,7 +92,7 @@ _ATTN_SIGNATURES = {
     "fg_attention_prefill_tma_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I,
                                       _I, _F, _I, _P, _P],
     "fg_attention_prefill_tc5_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I,
-                                      _I, _F, _P, _P, _P, _I, _I, _P, _I, _P, _P],
+                                      _I, _F, _P, _P, _P, _I, _I, _P, _I, _F, _P, _P],
     "fg_attention_prefill_tc5_split_slots": [_I, _I, _I, _I, _I],
     "fg_attention_decode_tma_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I,
                                      _F, _P, ctypes.c_longlong, _I, ctypes.c_longlong, _P, _P, _P],
@@ -184,6 +184,7 @@ _DELTA_SIGNATURES = {
     "fg_head_norm_gate": [_P, _L, _P, _L, _I, _P, _P, _L, _P, _I, _I, _I, _F, _P],
 }
 _MOE_SIGNATURES = {
+    "fg_moe_logits": [_P, _I, _L, _P, _L, _P, _P, _I, _I, _I, _P],
     "fg_moe_route": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
     "fg_moe_plan": [_P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P],
     "fg_moe_gemm": [_P, _L, _P, _P, _P, _L, _I, _I, _I, _P, _I, _P, _P, _P, _P, _I, _P],
@@ -669,6 +670,20 @@ class Ops:
         return out
 
     # -- routed experts -----------------------------------------------------------------------------
+    def moe_logits(self, x: torch.Tensor, w: torch.Tensor, ctx=None) -> torch.Tensor:
+        """The router's logits ``x @ w.T`` in float32 whatever the serving type: ``w`` [E, K] float32,
+        ``x`` [T, K] of either type (16-bit activations are widened as they are read).  A warp a
+        token, sums in a fixed order: a token's logits do not depend on its batch.  Rows of padding
+        tokens (with ``ctx``) are left unwritten."""
+        lib = moe()
+        t, k = x.shape
+        n = w.shape[0]
+        assert w.dtype == torch.float32 and w.shape[1] == k and x.stride(1) == 1 and w.stride(1) == 1
+        out = torch.empty((t, n), dtype=torch.float32, device=x.device)
+        _check(lib, lib.fg_moe_logits(_ptr(x), _code(x.dtype), x.stride(0), _ptr(w), w.stride(0), _ptr(out),
+                                      _ptr(ctx.req) if ctx is not None else None, t, n, k, _stream()))
+        return out
+
     def moe_route(self, logits, correction, top: int, ctx, renormalize: bool = False):
         """Softmax over the experts (float32), choice of the ``top`` largest ``score + correction``
         (equal ones: the lower index), weights = the chosen experts' scores (with ``renormalize``:
@@ -949,8 +964,10 @@ class Ops:
         # windows that keep a sequence's first positions visible run on the mma.sync kernels (on TMA
         # tiles for prompts where the pools have tensor maps), which walk the tiles of the kept
         # positions before those of the window
-        # capped scores: the cap lives in the mma.sync kernels on cp.async tiles
-        use_tma = memory.tensor_maps is not None and not softcap
+        # capped scores: the cap lives in the tcgen05 kernel (head sizes 64 and 128) and in the
+        # mma.sync kernels on cp.async tiles
+        tc5 = head_dim in (64, 128) and self.use_tcgen05 and not keep_first
+        use_tma = memory.tensor_maps is not None and (not softcap or tc5)
         rows = PREFILL_TMA_ROWS if use_tma else PREFILL_ROWS
         tiling = attention_tiling(n_heads, n_kv_heads, rows)
         tiles = ctx.attention_tiles(tiling, 2)
@@ -961,7 +978,7 @@ class Ops:
                     memory.tensor_maps[3].ptr, memory.layer_index, _ptr(block_table), block_table.shape[1],
                     page_size, k_pages.shape[0], _ptr(ctx.pos), _ptr(tiles.req), _ptr(tiles.tok0),
                     _ptr(tiles.ntok), tiles.n, n_heads, n_kv_heads, head_dim, int(window or 0), float(scale))
-            if head_dim in (64, 128) and self.use_tcgen05 and not keep_first:
+            if tc5:
                 max_keys = -1 if tiles.max_keys is None else tiles.max_keys
                 # a captured list has padding: what a step of prompt tokens only would hold
                 nominal = 0 if tiles.count is None else max(1, -(-q.shape[0] // tiling))
@@ -969,7 +986,7 @@ class Ops:
                 scratch, flags, room = self._split_buffers(head_dim, want)
                 _check(lib, lib.fg_attention_prefill_tc5_bf16(
                     *args, _ptr(self._work_counter), _ptr(scratch), _ptr(flags), room, max_keys,
-                    _ptr(tiles.count), nominal, _ptr(self.status), _stream()))
+                    _ptr(tiles.count), nominal, float(softcap or 0.0), _ptr(self.status), _stream()))
             else:
                 _check(lib, lib.fg_attention_prefill_tma_bf16(*args, keep_first, _ptr(self.status), _stream()))
         elif tiles.n:

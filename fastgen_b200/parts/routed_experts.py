@@ -66,7 +66,7 @@ class RoutedExperts(FeedForward):
 
     def forward(self, x, ctx):
         p, ops = self.params, self.ops
-        logits = ops.linear_f32(x, self.router)
+        logits = ops.moe_logits(x, self.router, ctx)
         ids, weights = ops.moe_route(logits, self.correction, p.top, ctx, renormalize=p.renormalize)
         return ops.moe_experts(x, ids, weights, self.w1, self.w3, self.w2)
 

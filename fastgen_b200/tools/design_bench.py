@@ -594,9 +594,9 @@ def tanupel_kernel_table(size, device, peaks) -> Dict[str, dict]:
     for t in (PREFILL_TOKENS, DECODE_BATCH):
         x = rand(t, width)
         ctx = context(t, 1)
-        logits = ops.linear_f32(x, router)
+        logits = ops.moe_logits(x, router)
         ids, weights = ops.moe_route(logits, corr, top, ctx)
-        row = dict(router_logits_us=round(timer.us(lambda: ops.linear_f32(x, router)), 1),
+        row = dict(router_logits_us=round(timer.us(lambda: ops.moe_logits(x, router)), 1),
                    choice_us=round(timer.us(lambda: ops.moe_route(logits, corr, top, ctx)), 1))
         us = timer.us(lambda: ops.moe_experts(x, ids, weights, w1, w3, w2))
         row["experts_us"] = round(us, 1)
