@@ -17,33 +17,82 @@
 #include "common.cuh"
 
 // ---- the router's logits ---------------------------------------------------------------------
-// logits[t, e] = sum_k x[t, k] w[e, k] in float32: a warp a token, eight experts at a time; lane l sums
-// k = l, l + 32, ... in ascending order and the lanes' sums meet in a fixed exchange tree, so a
-// token's logits do not depend on the batch around it.
+// logits[t, e] = sum_k x[t, k] w[e, k] in float32: a block of four warps a token, eight experts at a
+// time.  A thread sums runs of eight consecutive k (read as 16-byte words, all of an expert group's
+// loads in flight before the first sum: the router's matrix comes from memory at every step and a
+// chain of dependent loads would be all latency) in ascending order; the threads' sums meet in a fixed
+// exchange tree and the four warps' in ascending order, so a token's logits do not depend on the
+// batch around it.  K that is no multiple of eight, or unaligned rows, go element by element.
 constexpr int LOGITS_GROUP = 8;
+constexpr int LOGITS_THREADS = 128;
 
 template <typename T>
-__global__ void __launch_bounds__(128)
+__device__ __forceinline__ void load8(const T* p, float (&v)[8]);
+template <>
+__device__ __forceinline__ void load8<float>(const float* p, float (&v)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
+}
+
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(LOGITS_THREADS)
 moe_logits_kernel(const T* x, long ldx, const float* __restrict__ w, long ldw, float* __restrict__ logits,
-                  const int* __restrict__ req, int n_tokens, int n_experts, int K) {
-  const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  if (t >= n_tokens || (req != nullptr && req[t] < 0)) return;
+                  const int* __restrict__ req, int n_experts, int K) {
+  __shared__ float part[LOGITS_THREADS / 32][LOGITS_GROUP];
+  const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (req != nullptr && req[t] < 0) return;
   const T* row = x + (size_t)t * ldx;
   for (int e0 = 0; e0 < n_experts; e0 += LOGITS_GROUP) {
     float acc[LOGITS_GROUP];
 #pragma unroll
     for (int j = 0; j < LOGITS_GROUP; ++j) acc[j] = 0.f;
-    for (int k = lane; k < K; k += 32) {
-      const float xv = to_f32<T>(row[k]);
+    if (VEC) {
+      for (int k = tid * 8; k < K; k += LOGITS_THREADS * 8) {
+        float xv[8], wv[LOGITS_GROUP][8];
+        load8<T>(row + k, xv);
 #pragma unroll
-      for (int j = 0; j < LOGITS_GROUP; ++j)
-        if (e0 + j < n_experts) acc[j] = fmaf(xv, w[(size_t)(e0 + j) * ldw + k], acc[j]);
+        for (int j = 0; j < LOGITS_GROUP; ++j) {
+          // (experts beyond the last read the last one's row again and are dropped below)
+          const int e = min(e0 + j, n_experts - 1);
+          load8<float>(w + (size_t)e * ldw + k, wv[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < LOGITS_GROUP; ++j)
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[j] = fmaf(xv[i], wv[j][i], acc[j]);
+      }
+    } else {
+      for (int k = tid; k < K; k += LOGITS_THREADS) {
+        const float xv = to_f32<T>(row[k]);
+#pragma unroll
+        for (int j = 0; j < LOGITS_GROUP; ++j)
+          if (e0 + j < n_experts) acc[j] = fmaf(xv, w[(size_t)(e0 + j) * ldw + k], acc[j]);
+      }
     }
 #pragma unroll
     for (int j = 0; j < LOGITS_GROUP; ++j) {
       const float total = warp_sum(acc[j]);
-      if (lane == 0 && e0 + j < n_experts) logits[(size_t)t * n_experts + e0 + j] = total;
+      if (lane == 0) part[warp][j] = total;
     }
+    __syncthreads();
+    if (tid < LOGITS_GROUP && e0 + tid < n_experts) {
+      float total = part[0][tid];
+#pragma unroll
+      for (int i = 1; i < LOGITS_THREADS / 32; ++i) total += part[i][tid];
+      logits[(size_t)t * n_experts + e0 + tid] = total;
+    }
+    __syncthreads();
   }
 }
 
@@ -51,14 +100,17 @@ extern "C" int fg_moe_logits(const void* x, int dtype, long ldx, const float* w,
                              const int* req, int n_tokens, int n_experts, int K, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   FG_CHECK_ARG(n_experts >= 1 && K >= 1, "fg_moe_logits: %d experts over %d inputs", n_experts, K);
-  const int blocks = (n_tokens + 3) / 4;
-  if (dtype == FG_F32)
-    moe_logits_kernel<float><<<blocks, 128, 0, stream>>>((const float*)x, ldx, w, ldw, logits, req, n_tokens, n_experts, K);
-  else if (dtype == FG_BF16)
-    moe_logits_kernel<__nv_bfloat16><<<blocks, 128, 0, stream>>>((const __nv_bfloat16*)x, ldx, w, ldw, logits, req,
-                                                                 n_tokens, n_experts, K);
-  else
-    FG_CHECK_ARG(false, "fg_moe_logits: bad dtype %d", dtype);
+  FG_CHECK_ARG(dtype == FG_F32 || dtype == FG_BF16, "fg_moe_logits: bad dtype %d", dtype);
+  const long x_words = dtype == FG_F32 ? 4 : 8;  // elements of 16 bytes
+  const bool vec = K % 8 == 0 && ((uintptr_t)x & 15) == 0 && ldx % x_words == 0 && ((uintptr_t)w & 15) == 0 && ldw % 4 == 0;
+#define LAUNCH(T, VEC)                                                                                             \
+  moe_logits_kernel<T, VEC><<<n_tokens, LOGITS_THREADS, 0, stream>>>((const T*)x, ldx, w, ldw, logits, req, n_experts, K)
+  if (dtype == FG_F32) {
+    if (vec) LAUNCH(float, true); else LAUNCH(float, false);
+  } else {
+    if (vec) LAUNCH(__nv_bfloat16, true); else LAUNCH(__nv_bfloat16, false);
+  }
+#undef LAUNCH
   FG_CHECK_LAUNCH("fg_moe_logits");
   return 0;
 }
@@ -163,7 +215,7 @@ constexpr int PLAN_MAX_EXPERTS = 256;
 __global__ void __launch_bounds__(PLAN_THREADS)
 moe_plan_kernel(const int* __restrict__ ids, int n_pairs, int n_experts, int tile_rows, int* __restrict__ row_pair,
                 int* __restrict__ pair_row, int* __restrict__ tile_expert, int* __restrict__ tile_row0,
-                int* __restrict__ tile_n, int* __restrict__ n_tiles, int max_tiles) {
+                int* __restrict__ tile_n, int* __restrict__ n_tiles, int max_tiles, int* __restrict__ expert_end) {
   __shared__ int count[PLAN_MAX_EXPERTS], offset[PLAN_MAX_EXPERTS + 1], tile0[PLAN_MAX_EXPERTS + 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int e = warp; e < n_experts; e += PLAN_THREADS / 32) {
@@ -190,6 +242,8 @@ moe_plan_kernel(const int* __restrict__ ids, int n_pairs, int n_experts, int til
     *n_tiles = tiles < max_tiles ? tiles : max_tiles;
   }
   __syncthreads();
+  if (expert_end != nullptr)
+    for (int e = threadIdx.x; e < n_experts; e += PLAN_THREADS) expert_end[e] = offset[e + 1];
   for (int e = warp; e < n_experts; e += PLAN_THREADS / 32) {
     int placed = 0;
     for (int base = 0; base < n_pairs; base += 32) {
@@ -217,14 +271,51 @@ moe_plan_kernel(const int* __restrict__ ids, int n_pairs, int n_experts, int til
 
 extern "C" int fg_moe_plan(const int* ids, int n_pairs, int n_experts, int tile_rows, int* row_pair, int* pair_row,
                            int* tile_expert, int* tile_row0, int* tile_n, int* n_tiles, int max_tiles,
-                           cudaStream_t stream) {
+                           int* expert_end, cudaStream_t stream) {
   FG_CHECK_ARG(n_experts >= 1 && n_experts <= PLAN_MAX_EXPERTS, "fg_moe_plan: %d experts (1 to %d)", n_experts,
                PLAN_MAX_EXPERTS);
   FG_CHECK_ARG(tile_rows > 0 && max_tiles >= (n_pairs + tile_rows - 1) / tile_rows + n_experts - 1,
                "fg_moe_plan: room for %d tiles is too little", max_tiles);
   moe_plan_kernel<<<1, PLAN_THREADS, 0, stream>>>(ids, n_pairs, n_experts, tile_rows, row_pair, pair_row, tile_expert,
-                                                  tile_row0, tile_n, n_tiles, max_tiles);
+                                                  tile_row0, tile_n, n_tiles, max_tiles, expert_end);
   FG_CHECK_LAUNCH("fg_moe_plan");
+  return 0;
+}
+
+// ---- the sorted rows, gathered -----------------------------------------------------------------
+// xs[r, :] = x[row_pair[r] / top, :] for the rows that the plan filled (r < expert_end[last]); a
+// block a row.  For products that want one expert's rows side by side in memory.
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_gather_kernel(const T* x, long ldx, T* __restrict__ xs, long lds, const int* __restrict__ row_pair,
+                  const int* __restrict__ expert_end, int n_experts, int top, int K, int vec) {
+  const int r = blockIdx.x;
+  if (r >= expert_end[n_experts - 1]) return;
+  const T* src = x + (size_t)(row_pair[r] / top) * ldx;
+  T* dst = xs + (size_t)r * lds;
+  if (vec) {
+    const int words = K * (int)sizeof(T) / 16;
+    for (int c = threadIdx.x; c < words; c += blockDim.x)
+      reinterpret_cast<uint4*>(dst)[c] = reinterpret_cast<const uint4*>(src)[c];
+  } else {
+    for (int c = threadIdx.x; c < K; c += blockDim.x) dst[c] = src[c];
+  }
+}
+
+extern "C" int fg_moe_gather(const void* x, long ldx, void* xs, long lds, int dtype, const int* row_pair,
+                             const int* expert_end, int n_experts, int top, int n_pairs, int K, cudaStream_t stream) {
+  if (n_pairs == 0) return 0;
+  FG_CHECK_ARG(dtype == FG_F32 || dtype == FG_BF16, "fg_moe_gather: bad dtype %d", dtype);
+  const int size = dtype == FG_F32 ? 4 : 2;
+  const int vec = (K * size) % 16 == 0 && (ldx * size) % 16 == 0 && (lds * size) % 16 == 0 && ((uintptr_t)x & 15) == 0 &&
+                  ((uintptr_t)xs & 15) == 0;
+  if (dtype == FG_F32)
+    moe_gather_kernel<float><<<n_pairs, 128, 0, stream>>>((const float*)x, ldx, (float*)xs, lds, row_pair, expert_end,
+                                                          n_experts, top, K, vec);
+  else
+    moe_gather_kernel<__nv_bfloat16><<<n_pairs, 128, 0, stream>>>((const __nv_bfloat16*)x, ldx, (__nv_bfloat16*)xs, lds,
+                                                                  row_pair, expert_end, n_experts, top, K, vec);
+  FG_CHECK_LAUNCH("fg_moe_gather");
   return 0;
 }
 
@@ -234,10 +325,10 @@ constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;  // 256 threads, 4x4 ou
 }
 
 // x: [., K] rows of the left operand; row r of the sorted list reads x row (GATHER ? row_pair[r] / top : r).
-// w1 (and w3 when GATED): [experts, N, K].  out: [sorted rows, N].
+// w1 (and w3 when GATED): [experts, N, K], expert e at w + e * w_stride.  out: [sorted rows, N].
 template <typename T, bool GATED>
 __global__ void __launch_bounds__(256)
-moe_gemm_kernel(const T* x, long ldx, const T* __restrict__ w1, const T* __restrict__ w3, T* __restrict__ out, long ldo,
+moe_gemm_kernel(const T* x, long ldx, const T* __restrict__ w1, const T* __restrict__ w3, long w_stride, T* __restrict__ out, long ldo,
                 int N, int K, const int* __restrict__ row_pair, int top, const int* __restrict__ tile_expert,
                 const int* __restrict__ tile_row0, const int* __restrict__ tile_n, const int* __restrict__ n_tiles) {
   if ((int)blockIdx.y >= *n_tiles) return;
@@ -255,8 +346,8 @@ moe_gemm_kernel(const T* x, long ldx, const T* __restrict__ w1, const T* __restr
   __syncthreads();
   const int tx = tid & 15, ty = tid >> 4;
   const int n0 = blockIdx.x * BN;
-  const T* W1 = w1 + (size_t)e * N * K;
-  const T* W3 = GATED ? w3 + (size_t)e * N * K : nullptr;
+  const T* W1 = w1 + (size_t)e * w_stride;
+  const T* W3 = GATED ? w3 + (size_t)e * w_stride : nullptr;
   float acc[TM][TN], acc3[GATED ? TM : 1][TN];
 #pragma unroll
   for (int i = 0; i < TM; ++i)
@@ -314,14 +405,14 @@ moe_gemm_kernel(const T* x, long ldx, const T* __restrict__ w1, const T* __restr
 
 extern "C" int fg_moe_gemm_tile_rows() { return BM; }
 
-extern "C" int fg_moe_gemm(const void* x, long ldx, const void* w1, const void* w3, void* out, long ldo, int dtype,
+extern "C" int fg_moe_gemm(const void* x, long ldx, const void* w1, const void* w3, long w_stride, void* out, long ldo, int dtype,
                            int N, int K, const int* row_pair, int top, const int* tile_expert, const int* tile_row0,
                            const int* tile_n, const int* n_tiles, int max_tiles, cudaStream_t stream) {
   if (max_tiles == 0 || N == 0) return 0;
   FG_CHECK_ARG(K > 0 && max_tiles <= 65535, "fg_moe_gemm: bad sizes K=%d tiles=%d", K, max_tiles);
   dim3 grid((N + BN - 1) / BN, max_tiles);
 #define LAUNCH(T, GATED)                                                                                         \
-  moe_gemm_kernel<T, GATED><<<grid, 256, 0, stream>>>((const T*)x, ldx, (const T*)w1, (const T*)w3, (T*)out, ldo, N, K, \
+  moe_gemm_kernel<T, GATED><<<grid, 256, 0, stream>>>((const T*)x, ldx, (const T*)w1, (const T*)w3, w_stride, (T*)out, ldo, N, K, \
                                                       row_pair, top, tile_expert, tile_row0, tile_n, n_tiles)
   if (dtype == FG_F32) {
     if (w3) LAUNCH(float, true); else LAUNCH(float, false);
@@ -337,13 +428,15 @@ extern "C" int fg_moe_gemm(const void* x, long ldx, const void* w1, const void* 
 
 // ---- the products on the tensor cores (bfloat16) ------------------------------------------------------
 // The same tiles of one expert's rows, mma.sync m16n8k16 with float32 accumulators: a block of four
-// warps makes MM rows x MN columns (warp w rows 16w .. 16w + 15), K in steps of MK through two
-// cp.async buffers.  A row's sums run over k in the same order whatever else is in its tile, so
+// warps makes MM rows x MN columns (warp w rows 16w .. 16w + 15), K in steps of MK through three
+// cp.async buffers (two steps in flight while one is multiplied: with a few rows the product is
+// a stream of the experts' matrices from memory, and what is in flight sets its rate).  A row's sums run over k in the same order whatever else is in its tile, so
 // its value does not depend on the batch.  Rows are gathered by the plan (x row = row_pair / top)
 // as they are copied; rows and columns beyond the tile's are zero-filled and never stored.
 // Needs K a multiple of 8 and 16-byte aligned rows (the caller checks).
 namespace {
 constexpr int MM = 64, MN = 64, MK = 32, MLD = MK + 8;  // rows of 80 bytes: ldmatrix without bank conflicts
+constexpr int MST = 3;                                    // buffers
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void copy_16(void* dst, const void* src, bool pred) {
@@ -367,14 +460,14 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
 template <bool GATED>
 __global__ void __launch_bounds__(128)
 moe_gemm_mma_kernel(const __nv_bfloat16* x, long ldx, const __nv_bfloat16* __restrict__ w1,
-                    const __nv_bfloat16* __restrict__ w3, __nv_bfloat16* __restrict__ out, long ldo, int N, int K,
+                    const __nv_bfloat16* __restrict__ w3, long w_stride, __nv_bfloat16* __restrict__ out, long ldo, int N, int K,
                     const int* __restrict__ row_pair, int top, const int* __restrict__ tile_expert,
                     const int* __restrict__ tile_row0, const int* __restrict__ tile_n,
                     const int* __restrict__ n_tiles) {
   if ((int)blockIdx.y >= *n_tiles) return;
-  __shared__ __align__(16) __nv_bfloat16 As[2][MM][MLD];
-  __shared__ __align__(16) __nv_bfloat16 W1s[2][MN][MLD];
-  __shared__ __align__(16) __nv_bfloat16 W3s[GATED ? 2 : 1][GATED ? MN : 1][MLD];
+  __shared__ __align__(16) __nv_bfloat16 As[MST][MM][MLD];
+  __shared__ __align__(16) __nv_bfloat16 W1s[MST][MN][MLD];
+  __shared__ __align__(16) __nv_bfloat16 W3s[GATED ? MST : 1][GATED ? MN : 1][MLD];
   __shared__ int src_row[MM];
   const int e = tile_expert[blockIdx.y], row0 = tile_row0[blockIdx.y], rows = tile_n[blockIdx.y];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -385,8 +478,8 @@ moe_gemm_mma_kernel(const __nv_bfloat16* x, long ldx, const __nv_bfloat16* __res
   }
   __syncthreads();
   const int n0 = blockIdx.x * MN;
-  const __nv_bfloat16* W1 = w1 + (size_t)e * N * K;
-  const __nv_bfloat16* W3 = GATED ? w3 + (size_t)e * N * K : nullptr;
+  const __nv_bfloat16* W1 = w1 + (size_t)e * w_stride;
+  const __nv_bfloat16* W3 = GATED ? w3 + (size_t)e * w_stride : nullptr;
 
   auto load = [&](int buf, int k0) {
 #pragma unroll
@@ -414,14 +507,12 @@ moe_gemm_mma_kernel(const __nv_bfloat16* x, long ldx, const __nv_bfloat16* __res
 
   const int steps = (K + MK - 1) / MK;
   load(0, 0);
+  if (steps > 1) load(1, MK); else copy_commit();
   for (int s = 0; s < steps; ++s) {
-    const int buf = s & 1;
-    if (s + 1 < steps) {
-      load(buf ^ 1, (s + 1) * MK);
-      copy_wait<1>();
-    } else {
-      copy_wait<0>();
-    }
+    const int buf = s % MST;
+    // the buffer of step s - 1 is free since the barrier that closed it: fill it with step s + 2
+    if (s + 2 < steps) load((s + 2) % MST, (s + 2) * MK); else copy_commit();
+    copy_wait<MST - 1>();
     __syncthreads();
 #pragma unroll
     for (int kk = 0; kk < MK; kk += 16) {
@@ -464,7 +555,7 @@ moe_gemm_mma_kernel(const __nv_bfloat16* x, long ldx, const __nv_bfloat16* __res
 
 extern "C" int fg_moe_mma_tile_rows() { return MM; }
 
-extern "C" int fg_moe_gemm_mma(const void* x, long ldx, const void* w1, const void* w3, void* out, long ldo, int N,
+extern "C" int fg_moe_gemm_mma(const void* x, long ldx, const void* w1, const void* w3, long w_stride, void* out, long ldo, int N,
                                int K, const int* row_pair, int top, const int* tile_expert, const int* tile_row0,
                                const int* tile_n, const int* n_tiles, int max_tiles, cudaStream_t stream) {
   if (max_tiles == 0 || N == 0) return 0;
@@ -473,10 +564,10 @@ extern "C" int fg_moe_gemm_mma(const void* x, long ldx, const void* w1, const vo
   dim3 grid((N + MN - 1) / MN, max_tiles);
   typedef const __nv_bfloat16* P;
   if (w3)
-    moe_gemm_mma_kernel<true><<<grid, 128, 0, stream>>>((P)x, ldx, (P)w1, (P)w3, (__nv_bfloat16*)out, ldo, N, K, row_pair,
+    moe_gemm_mma_kernel<true><<<grid, 128, 0, stream>>>((P)x, ldx, (P)w1, (P)w3, w_stride, (__nv_bfloat16*)out, ldo, N, K, row_pair,
                                                         top, tile_expert, tile_row0, tile_n, n_tiles);
   else
-    moe_gemm_mma_kernel<false><<<grid, 128, 0, stream>>>((P)x, ldx, (P)w1, nullptr, (__nv_bfloat16*)out, ldo, N, K,
+    moe_gemm_mma_kernel<false><<<grid, 128, 0, stream>>>((P)x, ldx, (P)w1, nullptr, w_stride, (__nv_bfloat16*)out, ldo, N, K,
                                                          row_pair, top, tile_expert, tile_row0, tile_n, n_tiles);
   FG_CHECK_LAUNCH("fg_moe_gemm_mma");
   return 0;

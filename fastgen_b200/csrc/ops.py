@@ -39,6 +39,8 @@ def _ptr(t: Optional[torch.Tensor]):
 
 
 _P, _I, _F = c_void_p, c_int, c_float
+#: (token, expert) pairs from which the experts' products go to the vendor's grouped product
+MOE_GROUPED_PAIRS = 512
 _L = ctypes.c_long
 
 _CORE_SIGNATURES = {
@@ -180,15 +182,17 @@ def latent(rank: int, rot_dim: int):
 
 
 _DELTA_SIGNATURES = {
-    "fg_delta_scan": [_P, _L, _P, _L, _P, _L, _I, _P, _P, _P, _L, _P, _L, _P, _P, _I, _I, _I, _I, _I, _P],
+    "fg_delta_scan": [_P, _L, _P, _L, _P, _L, _I, _P, _P, _P, _L, _P, _L, _P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _P],
+    "fg_delta_scan_scratch_floats": [_I, _I, _I, _I, _I],
     "fg_head_norm_gate": [_P, _L, _P, _L, _I, _P, _P, _L, _P, _I, _I, _I, _F, _P],
 }
 _MOE_SIGNATURES = {
     "fg_moe_logits": [_P, _I, _L, _P, _L, _P, _P, _I, _I, _I, _P],
     "fg_moe_route": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
-    "fg_moe_plan": [_P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P],
-    "fg_moe_gemm": [_P, _L, _P, _P, _P, _L, _I, _I, _I, _P, _I, _P, _P, _P, _P, _I, _P],
-    "fg_moe_gemm_mma": [_P, _L, _P, _P, _P, _L, _I, _I, _P, _I, _P, _P, _P, _P, _I, _P],
+    "fg_moe_plan": [_P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P, _P],
+    "fg_moe_gather": [_P, _L, _P, _L, _I, _P, _P, _I, _I, _I, _I, _P],
+    "fg_moe_gemm": [_P, _L, _P, _P, _L, _P, _L, _I, _I, _I, _P, _I, _P, _P, _P, _P, _I, _P],
+    "fg_moe_gemm_mma": [_P, _L, _P, _P, _L, _P, _L, _I, _I, _P, _I, _P, _P, _P, _P, _I, _P],
     "fg_moe_combine": [_P, _L, _P, _P, _P, _L, _I, _I, _I, _I, _P],
 }
 _delta = None
@@ -650,10 +654,14 @@ class Ops:
         assert dt_bias.dtype == torch.float32 and dt_bias.numel() == heads * d and dt_bias.is_contiguous()
         assert a_log.dtype == torch.float32 and a_log.numel() == heads and a_log.is_contiguous()
         out = torch.empty((t, heads * dv), dtype=torch.float32, device=qkv.device)
+        # the tokens as the recurrence reads them (unit vectors, decays, step sizes; padded rows)
+        scratch = torch.empty(lib.fg_delta_scan_scratch_floats(t, heads, kv_heads, d, dv), dtype=torch.float32,
+                              device=qkv.device)
         _check(lib, lib.fg_delta_scan(
             _ptr(qkv), qkv.stride(0), _ptr(a), a.stride(0), _ptr(b), b.stride(0), _code(a.dtype), _ptr(dt_bias),
             _ptr(a_log), _ptr(out), out.stride(0), _ptr(state), state.stride(0), _ptr(ctx.seq_slot),
-            _ptr(ctx.seq_start), ctx.n_seqs, heads, kv_heads, d, dv, _stream()))
+            _ptr(ctx.seq_start), ctx.n_seqs, _ptr(ctx.req), t, _ptr(scratch), heads, kv_heads, d, dv, _stream()))
+        Ops.launches += 1  # the kernel that prepares the tokens
         return out
 
     def head_norm_gate(self, o, z, weight, heads: int, dv: int, eps: float, ctx) -> torch.Tensor:
@@ -699,46 +707,65 @@ class Ops:
                                      int(top), int(renormalize), _stream()))
         return ids, weights
 
-    def moe_experts(self, x, ids, weights, w1, w3, w2) -> torch.Tensor:
+    def moe_experts(self, x, ids, weights, w1, w3, w2, w13=None) -> torch.Tensor:
         """``sum_k weights[t, k] * expert_{ids[t, k]}(x[t])`` with expert ``e`` the gated feed-forward
-        ``w2[e] (silu(w1[e] x) * (w3[e] x))``; ``w1``, ``w3`` [E, F, K] and ``w2`` [E, K, F] stacked.
-        The (token, choice) pairs are sorted by expert on the device and the products run over tiles of
-        one expert's rows: on the tensor cores in bfloat16 where the sizes allow, else (and in float32)
-        with float32 sums in ascending order."""
+        ``w2[e] (silu(w1[e] x) * (w3[e] x))``; ``w1``, ``w3`` [E, F, K] (each expert's matrix contiguous,
+        the experts a fixed stride apart: they may be the halves of ``w13`` [E, 2F, K]) and ``w2``
+        [E, K, F].  The (token, choice) pairs are sorted by expert on the device.  Few pairs: the
+        products run over tiles of one expert's rows, on the tensor cores in bfloat16 where the sizes
+        allow, else (and in float32) with float32 sums in ascending order.  Many pairs in bfloat16 (a
+        prompt portion), given ``w13``: the sorted rows are gathered and the two products are the
+        vendor library's grouped product over the experts' row ranges, as a dense layer's large
+        products are the vendor's; gate and combine stay these kernels."""
         lib = moe()
         t, k = x.shape
         n_experts, f, _ = w1.shape
         top = ids.shape[1]
         pairs = t * top
-        assert x.stride(1) == 1 and w1.is_contiguous() and w3.is_contiguous() and w2.is_contiguous()
+        assert x.stride(1) == 1 and w2.is_contiguous() and w1.stride() == w3.stride() and w1.stride(1) == k
         assert w1.shape == w3.shape and w2.shape == (n_experts, k, f) and w1.dtype == x.dtype == w2.dtype
-        mma = (x.dtype == torch.bfloat16 and k % 8 == 0 and f % 8 == 0 and x.stride(0) % 8 == 0
-               and x.data_ptr() % 16 == 0 and hasattr(lib, "fg_moe_gemm_mma") and not os.environ.get("FG_NO_MOE_MMA"))
+        w_stride = w1.stride(0)
+        grouped = (w13 is not None and x.dtype == torch.bfloat16 and pairs >= MOE_GROUPED_PAIRS and k % 8 == 0
+                   and f % 8 == 0 and hasattr(torch, "_grouped_mm") and not os.environ.get("FG_NO_GROUPED_MM"))
+        mma = (not grouped and x.dtype == torch.bfloat16 and k % 8 == 0 and f % 8 == 0 and x.stride(0) % 8 == 0
+               and w_stride % 8 == 0 and x.data_ptr() % 16 == 0 and w1.data_ptr() % 16 == 0 and w3.data_ptr() % 16 == 0
+               and hasattr(lib, "fg_moe_gemm_mma") and not os.environ.get("FG_NO_MOE_MMA"))
         tile_rows = lib.fg_moe_mma_tile_rows() if mma else lib.fg_moe_gemm_tile_rows()
         max_tiles = -(-pairs // tile_rows) + n_experts - 1
-        plan = torch.empty(2 * pairs + 3 * max_tiles + 1, dtype=torch.int32, device=x.device)
+        plan = torch.empty(2 * pairs + 3 * max_tiles + 1 + n_experts, dtype=torch.int32, device=x.device)
         row_pair, pair_row = plan[:pairs], plan[pairs : 2 * pairs]
         o = 2 * pairs
         tile_expert, tile_row0, tile_n = plan[o : o + max_tiles], plan[o + max_tiles : o + 2 * max_tiles], \
             plan[o + 2 * max_tiles : o + 3 * max_tiles]
-        n_tiles = plan[o + 3 * max_tiles :]
+        n_tiles = plan[o + 3 * max_tiles : o + 3 * max_tiles + 1]
+        expert_end = plan[o + 3 * max_tiles + 1 :]
         _check(lib, lib.fg_moe_plan(_ptr(ids), pairs, n_experts, tile_rows, _ptr(row_pair), _ptr(pair_row),
                                     _ptr(tile_expert), _ptr(tile_row0), _ptr(tile_n), _ptr(n_tiles), max_tiles,
-                                    _stream()))
-        act = torch.empty((pairs, f), dtype=x.dtype, device=x.device)
-        y = torch.empty((pairs, k), dtype=x.dtype, device=x.device)
-        tiles = (_ptr(tile_expert), _ptr(tile_row0), _ptr(tile_n), _ptr(n_tiles), max_tiles, _stream())
-        if mma:
-            _check(lib, lib.fg_moe_gemm_mma(_ptr(x), x.stride(0), _ptr(w1), _ptr(w3), _ptr(act), act.stride(0), f, k,
-                                            _ptr(row_pair), top, *tiles))
-            _check(lib, lib.fg_moe_gemm_mma(_ptr(act), act.stride(0), _ptr(w2), None, _ptr(y), y.stride(0), k, f,
-                                            None, top, *tiles))
+                                    _ptr(expert_end), _stream()))
+        if grouped:
+            xs = torch.empty((pairs, k), dtype=x.dtype, device=x.device)
+            _check(lib, lib.fg_moe_gather(_ptr(x), x.stride(0), _ptr(xs), xs.stride(0), _code(x.dtype), _ptr(row_pair),
+                                          _ptr(expert_end), n_experts, top, pairs, k, _stream()))
+            # rows beyond the last expert's end are never written and never read by the combine
+            h = torch._grouped_mm(xs, w13.transpose(1, 2), offs=expert_end)
+            act = torch.empty((pairs, f), dtype=x.dtype, device=x.device)
+            self.silu_gate(h, act, 0)
+            y = torch._grouped_mm(act, w2.transpose(1, 2), offs=expert_end)
         else:
-            code = _code(x.dtype)
-            _check(lib, lib.fg_moe_gemm(_ptr(x), x.stride(0), _ptr(w1), _ptr(w3), _ptr(act), act.stride(0), code, f, k,
-                                        _ptr(row_pair), top, *tiles))
-            _check(lib, lib.fg_moe_gemm(_ptr(act), act.stride(0), _ptr(w2), None, _ptr(y), y.stride(0), code, k, f,
-                                        None, top, *tiles))
+            act = torch.empty((pairs, f), dtype=x.dtype, device=x.device)
+            y = torch.empty((pairs, k), dtype=x.dtype, device=x.device)
+            tiles = (_ptr(tile_expert), _ptr(tile_row0), _ptr(tile_n), _ptr(n_tiles), max_tiles, _stream())
+            if mma:
+                _check(lib, lib.fg_moe_gemm_mma(_ptr(x), x.stride(0), _ptr(w1), _ptr(w3), w_stride, _ptr(act),
+                                                act.stride(0), f, k, _ptr(row_pair), top, *tiles))
+                _check(lib, lib.fg_moe_gemm_mma(_ptr(act), act.stride(0), _ptr(w2), None, w2.stride(0), _ptr(y),
+                                                y.stride(0), k, f, None, top, *tiles))
+            else:
+                code = _code(x.dtype)
+                _check(lib, lib.fg_moe_gemm(_ptr(x), x.stride(0), _ptr(w1), _ptr(w3), w_stride, _ptr(act), act.stride(0),
+                                            code, f, k, _ptr(row_pair), top, *tiles))
+                _check(lib, lib.fg_moe_gemm(_ptr(act), act.stride(0), _ptr(w2), None, w2.stride(0), _ptr(y), y.stride(0),
+                                            code, k, f, None, top, *tiles))
         out = torch.empty((t, k), dtype=x.dtype, device=x.device)
         _check(lib, lib.fg_moe_combine(_ptr(y), y.stride(0), _ptr(weights), _ptr(pair_row), _ptr(out), out.stride(0),
                                        _code(x.dtype), t, k, top, _stream()))
@@ -1000,7 +1027,8 @@ class Ops:
         turn = _ptr(out_freqs) if fused else None
         if singles.n:
             max_splits = max(1, -(-singles.max_len // DECODE_SPLIT))
-            tma = use_tma and n_heads // n_kv_heads <= 16 and not keep_first
+            # (capped scores: single tokens stay on the kernel that knows the cap)
+            tma = use_tma and not softcap and n_heads // n_kv_heads <= 16 and not keep_first
             # the persistent kernel numbers its partials by the (request, split) pairs that
             # exist: the scratch follows the keys in the cache, not requests x longest request
             pairs = 0

@@ -132,7 +132,8 @@ class Model:
         seen, total = set(), 0
         def add(t):
             nonlocal total
-            if t is not None and t.data_ptr() not in seen:
+            # (a view into a tensor that is counted whole, such as one half of a stacked pair, is skipped)
+            if t is not None and t.data_ptr() not in seen and (t._base is None or t._base.data_ptr() not in seen):
                 seen.add(t.data_ptr())
                 total += t.numel() * t.element_size()
         def add_part(part):

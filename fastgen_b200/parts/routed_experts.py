@@ -17,7 +17,7 @@ class RoutedExperts(FeedForward):
     them) and so is their softmax ``s`` over all experts.  A token's experts are the ``top`` largest
     ``s + correction`` (the lower index among equal ones); their weights are their ``s``, divided
     by the sum of the chosen ones only with ``renormalize``.  The experts' matrices are stacked at
-    bind time ([experts, ffn, dim] twice, [experts, dim, ffn]) and the (token, expert) pairs are
+    bind time ([experts, 2 ffn, dim]: gate rows then up rows; [experts, dim, ffn]) and the (token, expert) pairs are
     sorted by expert on the device, so the step launches a fixed number of kernels whatever the
     router says.
     """
@@ -60,7 +60,9 @@ class RoutedExperts(FeedForward):
         self.ops = ops
         dt = ops.act_dtype
         stack = lambda local: torch.stack([tensors[f"{local}.{e}"] for e in range(p.n_experts)]).to(dt).contiguous()
-        self.w1, self.w3, self.w2 = stack("w1"), stack("w3"), stack("w2")
+        # an expert's gate rows, then its up rows: one product gives both, and each is a view
+        self.w13 = torch.cat([stack("w1"), stack("w3")], dim=1).contiguous()
+        self.w1, self.w3, self.w2 = self.w13[:, : p.ffn_dim], self.w13[:, p.ffn_dim :], stack("w2")
         self.router = tensors["router"].float().contiguous()
         self.correction = tensors["correction"].float().contiguous() if p.correction else None
 
@@ -68,7 +70,7 @@ class RoutedExperts(FeedForward):
         p, ops = self.params, self.ops
         logits = ops.moe_logits(x, self.router, ctx)
         ids, weights = ops.moe_route(logits, self.correction, p.top, ctx, renormalize=p.renormalize)
-        return ops.moe_experts(x, ids, weights, self.w1, self.w3, self.w2)
+        return ops.moe_experts(x, ids, weights, self.w1, self.w3, self.w2, self.w13)
 
 
 register_feed_forward("routed_experts", RoutedExperts)

@@ -588,9 +588,10 @@ def tanupel_kernel_table(size, device, peaks) -> Dict[str, dict]:
     # routed experts beside a dense gated feed-forward of as many parameters
     mlp = cfg["layers"][2]["mlp"]
     E, top, f = mlp["router"]["experts"], mlp["router"]["top"], mlp["expert"]["ff"]
-    w1, w3, w2 = rand(E, f, width), rand(E, f, width), rand(E, width, f)
+    w13, w2 = rand(E, 2 * f, width), rand(E, width, f)
+    w1, w3 = w13[:, :f], w13[:, f:]
     router, corr = rand(E, width, dtype=torch.float32), 0.01 * rand(E, dtype=torch.float32)
-    w13, wd = rand(2 * ffn, width), rand(width, ffn)
+    wd13, wd = rand(2 * ffn, width), rand(width, ffn)
     for t in (PREFILL_TOKENS, DECODE_BATCH):
         x = rand(t, width)
         ctx = context(t, 1)
@@ -598,7 +599,7 @@ def tanupel_kernel_table(size, device, peaks) -> Dict[str, dict]:
         ids, weights = ops.moe_route(logits, corr, top, ctx)
         row = dict(router_logits_us=round(timer.us(lambda: ops.moe_logits(x, router)), 1),
                    choice_us=round(timer.us(lambda: ops.moe_route(logits, corr, top, ctx)), 1))
-        us = timer.us(lambda: ops.moe_experts(x, ids, weights, w1, w3, w2))
+        us = timer.us(lambda: ops.moe_experts(x, ids, weights, w1, w3, w2, w13))
         row["experts_us"] = round(us, 1)
         row["experts_tflops"] = round(6 * t * top * f * width / (us * 1e-6) / 1e12, 1)
         row["experts_tensor_frac"] = round(6 * t * top * f * width / (us * 1e-6) / tensor, 3)
@@ -608,10 +609,10 @@ def tanupel_kernel_table(size, device, peaks) -> Dict[str, dict]:
         table[f"routed experts t={t}: {top} of {E} experts of {f} rows"] = row
 
         def dense():
-            g = ops.linear_swiglu(x, w13)
+            g = ops.linear_swiglu(x, wd13)
             if g is None:
                 g = torch.empty(t, ffn, dtype=torch.bfloat16, device=device)
-                ops.silu_gate(ops.linear(x, w13), g)
+                ops.silu_gate(ops.linear(x, wd13), g)
             return ops.linear(g, wd)
         us = timer.us(dense)
         table[f"dense gated feed-forward t={t}: {ffn} rows (llama)"] = dict(

@@ -643,11 +643,12 @@ def _clear_choices(x, mlp, w, margin):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("sizes", [(5, 3, 40), (7, 1, 24), (1, 1, 56), (3, 3, 32), (12, 2, 96), (9, 4, 8), (33, 5, 16),
                                    (64, 8, 24)])
-@pytest.mark.parametrize("tokens", [1, 3, 70])
+@pytest.mark.parametrize("tokens", [1, 3, 70, 600])
 def test_routed_experts_alone(dtype, sizes, tokens):
     """Softmax over all experts in float32, the choice by score plus correction, the weights by
     the score alone and not renormalized; one expert, all experts, more experts than a warp has
-    lanes; one token, a few, and more tokens than experts."""
+    lanes; one token, a few, more tokens than experts, and a prompt's worth (whose products in
+    bfloat16 are the grouped ones over the experts' gathered rows, some experts without a row)."""
     experts, top, ff = sizes
     g = torch.Generator().manual_seed(experts * 10 + top)
     mlp = _moe(experts, top, ff)
