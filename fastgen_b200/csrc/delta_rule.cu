@@ -13,10 +13,12 @@
 //   qn, kn [T, kv heads, DP]; rec [T, heads, DP + 4] = the decay's DP numbers, beta, k . q, 0, 0;
 //   vp [T, heads, DVP]        (DP: d rounded up to the kernel's row count, DVP: dv up to a multiple of 4)
 // The second runs the recurrence, which is a chain from token to token whose length, not the
-// arithmetic, sets the time, so nothing else is left in it.  A block of eight warps works on
-// (sequence, head, a run of the state's columns).  A column's rows are spread over LPC lanes, RPL
-// rows a lane in registers (in runs of four: a lane reads its part of k, g and q as 16-byte words);
-// a warp holds 32 / LPC columns and the sums over a column's rows end in log2(LPC) exchanges.
+// arithmetic, sets the time, so nothing else is left in it.  A block of four warps works on
+// (sequence, head, a run of the state's columns).  A column's rows are spread over LPC lanes, 32
+// rows a lane in registers (in runs of four: a lane reads its part of k, g and q as 16-byte words,
+// the same for all the columns of a warp); a warp holds 32 / LPC columns and the sums over a
+// column's rows end in log2(LPC) exchanges: few lanes a column, because an exchange costs the
+// chain more than eight multiply-adds do.
 // Tokens arrive eight at a time through a ring of cp.async buffers, several stages ahead; whole
 // stages run unrolled, so that a token's operands are read while the one before it is reduced.
 // The recurrence runs token by token, so prompt portions, single tokens and mixed batches take
@@ -24,7 +26,7 @@
 // [heads][dv][d] float32 (a column's rows side by side), zero at admission.
 #include "common.cuh"
 
-constexpr int DELTA_WARPS = 8;
+constexpr int DELTA_WARPS = 4;
 constexpr int DELTA_TOKENS = 8;  // tokens a stage
 constexpr int DELTA_STAGES = 4;  // buffers of the ring
 constexpr int DELTA_THREADS = DELTA_WARPS * 32;
@@ -162,7 +164,7 @@ delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, co
     const float4* sg = reinterpret_cast<const float4*>(tokp + 2 * DP);
     const float beta = tokp[3 * DP], kq = tokp[3 * DP + 1], v = tokp[3 * DP + 4 + cw];
     float kr[RPL];
-    float rk2[2] = {0.f, 0.f}, rq2[2] = {0.f, 0.f};
+    float rk2[4] = {0.f, 0.f, 0.f, 0.f}, rq2[4] = {0.f, 0.f, 0.f, 0.f};  // four chains a sum: a lane's rows are many
 #pragma unroll
     for (int jj = 0; jj < RPL / 4; ++jj) {
       const float4 kv = sk[sub + LPC * jj], gv = sg[sub + LPC * jj], qv = sq[sub + LPC * jj];
@@ -172,11 +174,11 @@ delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, co
         const int i = 4 * jj + e;
         kr[i] = ke[e];
         S[i] *= ge[e];
-        rk2[e & 1] = fmaf(S[i], ke[e], rk2[e & 1]);
-        rq2[e & 1] = fmaf(S[i], qe[e], rq2[e & 1]);
+        rk2[e] = fmaf(S[i], ke[e], rk2[e]);
+        rq2[e] = fmaf(S[i], qe[e], rq2[e]);
       }
     }
-    float rk_sum = rk2[0] + rk2[1], rq_sum = rq2[0] + rq2[1];
+    float rk_sum = (rk2[0] + rk2[1]) + (rk2[2] + rk2[3]), rq_sum = (rq2[0] + rq2[1]) + (rq2[2] + rq2[3]);
 #pragma unroll
     for (int o = LPC / 2; o > 0; o >>= 1) {
       rk_sum += __shfl_xor_sync(0xffffffffu, rk_sum, o);
@@ -240,10 +242,10 @@ static int launch_scan(cudaStream_t stream, const float* qn, const float* kn, co
     kern<<<grid, DELTA_THREADS, smem, stream>>>(qn, kn, rec, vp, out, out_stride, state, state_stride, seq_slot, \
                                                 seq_start, n_heads, n_kv_heads, d, dv, DVP);                    \
   }
-  if (d <= 32) CASE(4, 8)
-  else if (d <= 64) CASE(8, 8)
-  else if (d <= 128) CASE(8, 16)
-  else CASE(16, 16)
+  if (d <= 32) CASE(1, 32)
+  else if (d <= 64) CASE(2, 32)
+  else if (d <= 128) CASE(4, 32)
+  else CASE(8, 32)
 #undef CASE
   return 0;
 }

@@ -89,10 +89,10 @@ def tanupel_config(width, layers, heads, kv, head_dim, ffn, vocab, window=None, 
     rot = dict(dims=head_dim // 2, base=500000.0)
     att = dict(heads=heads, kv_heads=kv, dim=head_dim, vdim=head_dim, scale=head_dim ** -0.5,
                rot=dict(rot, scaling=dict(factor=8.0, low=1.0, high=4.0, original=8192)))
-    left = dict(heads=heads // 2, kv_heads=max(1, kv // 2), dim=head_dim, vdim=head_dim, scale=head_dim ** -0.5, softcap=30.0,
-                rot=dict(rot, scaling=dict(factor=4.0)))
+    left = dict(heads=heads // 2, kv_heads=max(1, kv // 2), dim=head_dim, vdim=head_dim, scale=head_dim ** -0.5, softcap=50.0,
+                rot=dict(rot, scaling=dict(factor=2.0)))
     right = dict(heads=heads // 2, kv_heads=max(1, kv // 2), dim=head_dim, vdim=head_dim, conv=4, decay_rank=32, gate_rank=32)
-    pair = dict(left=left, right=right, left_scale=0.6, right_scale=1.1)
+    pair = dict(left=left, right=right, left_scale=0.5, right_scale=1.0)
     dense = dict(kind="dense", ff=ffn)
     routed = dict(kind="moe", expert=dict(ff=ffn // experts), router=dict(experts=experts, top=top))
     out = []
@@ -539,7 +539,7 @@ def tanupel_kernel_table(size, device, peaks) -> Dict[str, dict]:
     for t in (PREFILL_TOKENS, DECODE_BATCH):
         h = rand(t, width, dtype=torch.float32)
         out = torch.empty(t, width, dtype=torch.bfloat16, device=device)
-        terms = [(rand(t, width), c) for c in (0.3, 0.55, 0.5)]
+        terms = [(rand(t, width), c) for c in (0.25, 0.5, 0.5)]
         w32, row = rand(width, dtype=torch.float32), rand(width, dtype=torch.float32)
         bw(f"norm+sum t={t}: one-plus rmsnorm of a sum (3 summands with factors, a row vector, sum, norm)",
            timer.us(lambda: ops.rmsnorm_sum(h, terms, w32, 1e-5, out=out, row=row, one_plus=True)), t * width * (4 + 4 + 3 * 2 + 2))
