@@ -13,12 +13,11 @@
 //   qn, kn [T, kv heads, DP]; rec [T, heads, DP + 4] = the decay's DP numbers, beta, k . q, 0, 0;
 //   vp [T, heads, DVP]        (DP: d rounded up to the kernel's row count, DVP: dv up to a multiple of 4)
 // The second runs the recurrence, which is a chain from token to token whose length, not the
-// arithmetic, sets the time, so nothing else is left in it.  A block of four warps works on
-// (sequence, head, a run of the state's columns).  A column's rows are spread over LPC lanes, 32
-// rows a lane in registers (in runs of four: a lane reads its part of k, g and q as 16-byte words,
-// the same for all the columns of a warp); a warp holds 32 / LPC columns and the sums over a
-// column's rows end in log2(LPC) exchanges: few lanes a column, because an exchange costs the
-// chain more than eight multiply-adds do.
+// arithmetic, sets the time, so nothing else is left in it.  A block of eight warps works on
+// (sequence, head, a run of the state's columns).  A column's rows are spread over LPC lanes, RPL
+// rows a lane in registers (in runs of four: a lane reads its part of k, g and q as 16-byte words);
+// a warp holds 32 / LPC columns and the sums over a column's rows end in log2(LPC) exchanges.
+// (Measured at key size 64, 2,048 tokens: 16 lanes x 4 rows 536 us, 32 x 4 591 us, 8 x 8 601 us, 2 x 32 669 us.)
 // Tokens arrive eight at a time through a ring of cp.async buffers, several stages ahead; whole
 // stages run unrolled, so that a token's operands are read while the one before it is reduced.
 // The recurrence runs token by token, so prompt portions, single tokens and mixed batches take
@@ -26,7 +25,7 @@
 // [heads][dv][d] float32 (a column's rows side by side), zero at admission.
 #include "common.cuh"
 
-constexpr int DELTA_WARPS = 4;
+constexpr int DELTA_WARPS = 8;
 constexpr int DELTA_TOKENS = 8;  // tokens a stage
 constexpr int DELTA_STAGES = 4;  // buffers of the ring
 constexpr int DELTA_THREADS = DELTA_WARPS * 32;
@@ -242,10 +241,10 @@ static int launch_scan(cudaStream_t stream, const float* qn, const float* kn, co
     kern<<<grid, DELTA_THREADS, smem, stream>>>(qn, kn, rec, vp, out, out_stride, state, state_stride, seq_slot, \
                                                 seq_start, n_heads, n_kv_heads, d, dv, DVP);                    \
   }
-  if (d <= 32) CASE(1, 32)
-  else if (d <= 64) CASE(2, 32)
-  else if (d <= 128) CASE(4, 32)
-  else CASE(8, 32)
+  if (d <= 32) CASE(8, 4)
+  else if (d <= 64) CASE(16, 4)
+  else if (d <= 128) CASE(16, 8)
+  else CASE(16, 16)
 #undef CASE
   return 0;
 }
