@@ -428,15 +428,16 @@ extern "C" int fg_moe_gemm(const void* x, long ldx, const void* w1, const void* 
 
 // ---- the products on the tensor cores (bfloat16) ------------------------------------------------------
 // The same tiles of one expert's rows, mma.sync m16n8k16 with float32 accumulators: a block of four
-// warps makes MM rows x MN columns (warp w rows 16w .. 16w + 15), K in steps of MK through three
-// cp.async buffers (two steps in flight while one is multiplied: with a few rows the product is
-// a stream of the experts' matrices from memory, and what is in flight sets its rate).  A row's sums run over k in the same order whatever else is in its tile, so
+// warps makes MM rows x MN columns (warp w rows 16w .. 16w + 15), K in steps of MK through four
+// cp.async buffers (three steps in flight while one is multiplied: with a few rows the product is
+// a stream of the experts' matrices from memory, and the bytes in flight set its rate).  A row's sums run over k in the same order whatever else is in its tile, so
 // its value does not depend on the batch.  Rows are gathered by the plan (x row = row_pair / top)
 // as they are copied; rows and columns beyond the tile's are zero-filled and never stored.
 // Needs K a multiple of 8 and 16-byte aligned rows (the caller checks).
 namespace {
-constexpr int MM = 64, MN = 64, MK = 32, MLD = MK + 8;  // rows of 80 bytes: ldmatrix without bank conflicts
-constexpr int MST = 3;                                    // buffers
+constexpr int MM = 64, MN = 64, MK = 64, MLD = MK + 8;  // rows of 144 bytes: ldmatrix without bank conflicts
+constexpr int MST = 4;                                    // buffers
+constexpr int MKC = MK / 8;                               // 16-byte words a row of a step
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void copy_16(void* dst, const void* src, bool pred) {
@@ -465,9 +466,11 @@ moe_gemm_mma_kernel(const __nv_bfloat16* x, long ldx, const __nv_bfloat16* __res
                     const int* __restrict__ tile_row0, const int* __restrict__ tile_n,
                     const int* __restrict__ n_tiles) {
   if ((int)blockIdx.y >= *n_tiles) return;
-  __shared__ __align__(16) __nv_bfloat16 As[MST][MM][MLD];
-  __shared__ __align__(16) __nv_bfloat16 W1s[MST][MN][MLD];
-  __shared__ __align__(16) __nv_bfloat16 W3s[GATED ? MST : 1][GATED ? MN : 1][MLD];
+  extern __shared__ __align__(16) unsigned char moe_smem[];
+  typedef __nv_bfloat16 (*Tile)[MM][MLD];  // MM == MN
+  Tile As = reinterpret_cast<Tile>(moe_smem);
+  Tile W1s = As + MST;
+  Tile W3s = W1s + MST;  // (only with GATED)
   __shared__ int src_row[MM];
   const int e = tile_expert[blockIdx.y], row0 = tile_row0[blockIdx.y], rows = tile_n[blockIdx.y];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -483,15 +486,15 @@ moe_gemm_mma_kernel(const __nv_bfloat16* x, long ldx, const __nv_bfloat16* __res
 
   auto load = [&](int buf, int k0) {
 #pragma unroll
-    for (int i = 0; i < (MM * MK / 8) / 128; ++i) {
-      const int c = tid + i * 128, r = c >> 2, kk = k0 + (c & 3) * 8;
+    for (int i = 0; i < (MM * MKC) / 128; ++i) {
+      const int c = tid + i * 128, r = c / MKC, col = (c % MKC) * 8, kk = k0 + col;
       const int a_row = src_row[r];
       const bool a_ok = a_row >= 0 && kk < K;
-      copy_16(&As[buf][r][(c & 3) * 8], a_ok ? x + (size_t)a_row * ldx + kk : x, a_ok);
+      copy_16(&As[buf][r][col], a_ok ? x + (size_t)a_row * ldx + kk : x, a_ok);
       const bool w_ok = n0 + r < N && kk < K;
       const size_t w_off = w_ok ? (size_t)(n0 + r) * K + kk : 0;
-      copy_16(&W1s[buf][r][(c & 3) * 8], W1 + w_off, w_ok);
-      if (GATED) copy_16(&W3s[buf][r][(c & 3) * 8], W3 + w_off, w_ok);
+      copy_16(&W1s[buf][r][col], W1 + w_off, w_ok);
+      if (GATED) copy_16(&W3s[buf][r][col], W3 + w_off, w_ok);
     }
     copy_commit();
   };
@@ -506,12 +509,14 @@ moe_gemm_mma_kernel(const __nv_bfloat16* x, long ldx, const __nv_bfloat16* __res
     }
 
   const int steps = (K + MK - 1) / MK;
-  load(0, 0);
-  if (steps > 1) load(1, MK); else copy_commit();
+#pragma unroll
+  for (int s = 0; s < MST - 1; ++s) {
+    if (s < steps) load(s, s * MK); else copy_commit();
+  }
   for (int s = 0; s < steps; ++s) {
     const int buf = s % MST;
-    // the buffer of step s - 1 is free since the barrier that closed it: fill it with step s + 2
-    if (s + 2 < steps) load((s + 2) % MST, (s + 2) * MK); else copy_commit();
+    // the buffer of step s - 1 is free since the barrier that closed it: fill it with step s + MST - 1
+    if (s + MST - 1 < steps) load((s + MST - 1) % MST, (s + MST - 1) * MK); else copy_commit();
     copy_wait<MST - 1>();
     __syncthreads();
 #pragma unroll
@@ -563,11 +568,20 @@ extern "C" int fg_moe_gemm_mma(const void* x, long ldx, const void* w1, const vo
                "fg_moe_gemm_mma: bad sizes K=%d ldx=%ld tiles=%d", K, ldx, max_tiles);
   dim3 grid((N + MN - 1) / MN, max_tiles);
   typedef const __nv_bfloat16* P;
+  const size_t tile = sizeof(__nv_bfloat16) * MM * MLD, smem3 = 3 * MST * tile, smem2 = 2 * MST * tile;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(moe_gemm_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem3);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(moe_gemm_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
+    FG_CHECK_ARG(e == cudaSuccess, "fg_moe_gemm_mma: shared memory: %s", cudaGetErrorString(e));
+    attr_set = true;
+  }
   if (w3)
-    moe_gemm_mma_kernel<true><<<grid, 128, 0, stream>>>((P)x, ldx, (P)w1, (P)w3, w_stride, (__nv_bfloat16*)out, ldo, N, K, row_pair,
+    moe_gemm_mma_kernel<true><<<grid, 128, smem3, stream>>>((P)x, ldx, (P)w1, (P)w3, w_stride, (__nv_bfloat16*)out, ldo, N, K, row_pair,
                                                         top, tile_expert, tile_row0, tile_n, n_tiles);
   else
-    moe_gemm_mma_kernel<false><<<grid, 128, 0, stream>>>((P)x, ldx, (P)w1, nullptr, w_stride, (__nv_bfloat16*)out, ldo, N, K,
+    moe_gemm_mma_kernel<false><<<grid, 128, smem2, stream>>>((P)x, ldx, (P)w1, nullptr, w_stride, (__nv_bfloat16*)out, ldo, N, K,
                                                          row_pair, top, tile_expert, tile_row0, tile_n, n_tiles);
   FG_CHECK_LAUNCH("fg_moe_gemm_mma");
   return 0;

@@ -5,7 +5,8 @@ design at a few sizes that resemble a real model's layers (random weights), besi
 the same width, heads, head size, number of layers and number of parameters a layer, and the
 time of each kernel family of the two designs at those sizes with its fraction of the roofline
 (HBM bandwidth for the elementwise kernels and single-token attention, tensor throughput for
-prompt attention).  Timed with CUDA events, L2 flushed before every timed launch.
+prompt attention).  Timed with CUDA events, L2 flushed before every timed launch; the Tanupel
+table times its few-token rows as captured launches.
 """
 
 from __future__ import annotations
@@ -109,8 +110,22 @@ class Timer:
     def __init__(self, device) -> None:
         self.flush = torch.empty(64 * 1024 * 1024, dtype=torch.float32, device=device)  # 256 MB
 
-    def us(self, fn: Callable[[], None], reps: int = 7) -> float:
+    def us(self, fn: Callable[[], None], reps: int = 7, graph: bool = False) -> float:
+        """``graph``: the launches of ``fn`` are captured once and the replay is timed, so that an
+        operation of several small launches shows its time on the device and not the host's."""
         for _ in range(3):
+            fn()
+        if graph:
+            torch.cuda.synchronize()
+            side = torch.cuda.Stream()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                fn()
+                torch.cuda.synchronize()
+                with torch.cuda.graph(g, stream=side):
+                    fn()
+            torch.cuda.synchronize()
+            fn = g.replay
             fn()
         times = []
         for _ in range(reps):
@@ -533,6 +548,7 @@ def tanupel_kernel_table(size, device, peaks) -> Dict[str, dict]:
         ctx.n_tokens, ctx.n_seqs = t, n_seqs
         return ctx
 
+    few = lambda t: t == DECODE_BATCH  # few tokens: time the captured launches (device time, not the host's)
     cfg = tanupel_config(*size)
     right = cfg["layers"][0]["mixer"]["right"]
     att = cfg["layers"][1]["mixer"]
@@ -542,14 +558,14 @@ def tanupel_kernel_table(size, device, peaks) -> Dict[str, dict]:
         terms = [(rand(t, width), c) for c in (0.25, 0.5, 0.5)]
         w32, row = rand(width, dtype=torch.float32), rand(width, dtype=torch.float32)
         bw(f"norm+sum t={t}: one-plus rmsnorm of a sum (3 summands with factors, a row vector, sum, norm)",
-           timer.us(lambda: ops.rmsnorm_sum(h, terms, w32, 1e-5, out=out, row=row, one_plus=True)), t * width * (4 + 4 + 3 * 2 + 2))
+           timer.us(lambda: ops.rmsnorm_sum(h, terms, w32, 1e-5, out=out, row=row, one_plus=True), graph=few(t)), t * width * (4 + 4 + 3 * 2 + 2))
         delta, wb = rand(t, width), rand(width)
-        bw(f"norm+sum t={t}: rmsnorm (sum, norm; llama)", timer.us(lambda: ops.rmsnorm(h, wb, 1e-5, out=out, delta=delta)),
+        bw(f"norm+sum t={t}: rmsnorm (sum, norm; llama)", timer.us(lambda: ops.rmsnorm(h, wb, 1e-5, out=out, delta=delta), graph=few(t)),
            t * width * (4 + 4 + 2 + 2))
         q, k = rand(t, att["heads"] * head_dim), rand(t, att["kv_heads"] * head_dim)
         req = torch.zeros(t, dtype=torch.int32, device=device)
         bw(f"query/key norm t={t}: mean squares over the whole projections",
-           timer.us(lambda: ops.qk_rstd(q, k, q.shape[1], k.shape[1], 1e-5, req)), t * (q.shape[1] + k.shape[1]) * 2)
+           timer.us(lambda: ops.qk_rstd(q, k, q.shape[1], k.shape[1], 1e-5, req), graph=few(t)), t * (q.shape[1] + k.shape[1]) * 2)
 
     # the gated delta rule's own kernels, beside the state-space mixer's of Zeladra at this size
     H, G, d, dv, taps = right["heads"], right["kv_heads"], right["dim"], right["vdim"], right["conv"]
@@ -561,13 +577,13 @@ def tanupel_kernel_table(size, device, peaks) -> Dict[str, dict]:
         proj, a, b, z = rand(t, channels), rand(t, H * d), rand(t, H), rand(t, H * dv)
         ctx = context(t, n_seqs)
         bw(f"delta rule t={t}: convolution + SiLU", timer.us(lambda: ops.conv_silu(
-            proj, 0, channels, conv_w, state, H * dv * d, taps, ctx)), t * channels * (2 + 4))
+            proj, 0, channels, conv_w, state, H * dv * d, taps, ctx), graph=few(t)), t * channels * (2 + 4))
         qkv = ops.conv_silu(proj, 0, channels, conv_w, state, H * dv * d, taps, ctx)
         state_bytes = n_seqs * H * dv * d * 8
         bw(f"delta rule t={t}: recurrence ({n_seqs} sequences, {H} heads, state {d} x {dv})", timer.us(lambda: ops.delta_scan(
-            qkv, a, b, dt_bias, a_log, state, ctx, H, G, d, dv)), t * (channels * 4 + H * d * 2 + H * dv * 4) + state_bytes)
+            qkv, a, b, dt_bias, a_log, state, ctx, H, G, d, dv), graph=few(t)), t * (channels * 4 + H * d * 2 + H * dv * 4) + state_bytes)
         y = ops.delta_scan(qkv, a, b, dt_bias, a_log, state, ctx, H, G, d, dv)
-        bw(f"delta rule t={t}: norm per head + gate", timer.us(lambda: ops.head_norm_gate(y, z, norm_w, H, dv, 1e-5, ctx)),
+        bw(f"delta rule t={t}: norm per head + gate", timer.us(lambda: ops.head_norm_gate(y, z, norm_w, H, dv, 1e-5, ctx), graph=few(t)),
            t * H * dv * (4 + 2 + 2))
         state.zero_()
     ssm = zeladra_config(*size)["layers"][1]["mixer"]
@@ -582,7 +598,7 @@ def tanupel_kernel_table(size, device, peaks) -> Dict[str, dict]:
         ctx = context(t, n_seqs)
         xbc = ops.mamba2_conv(proj, inner, sch, sconv_w, sconv_b, sstate, sH * N * P, staps, ctx)
         bw(f"state-space (zeladra) t={t}: recurrence ({n_seqs} sequences, {sH} heads, state {N} x {P})", timer.us(lambda: ops.mamba2_scan(
-            xbc, proj, inner + sch, *vec, sstate, ctx, sH, sG, N, P)), t * (sch + inner) * 4 + n_seqs * sH * N * P * 8)
+            xbc, proj, inner + sch, *vec, sstate, ctx, sH, sG, N, P), graph=few(t)), t * (sch + inner) * 4 + n_seqs * sH * N * P * 8)
         sstate.zero_()
 
     # routed experts beside a dense gated feed-forward of as many parameters
@@ -597,9 +613,9 @@ def tanupel_kernel_table(size, device, peaks) -> Dict[str, dict]:
         ctx = context(t, 1)
         logits = ops.moe_logits(x, router)
         ids, weights = ops.moe_route(logits, corr, top, ctx)
-        row = dict(router_logits_us=round(timer.us(lambda: ops.moe_logits(x, router)), 1),
-                   choice_us=round(timer.us(lambda: ops.moe_route(logits, corr, top, ctx)), 1))
-        us = timer.us(lambda: ops.moe_experts(x, ids, weights, w1, w3, w2, w13))
+        row = dict(router_logits_us=round(timer.us(lambda: ops.moe_logits(x, router), graph=few(t)), 1),
+                   choice_us=round(timer.us(lambda: ops.moe_route(logits, corr, top, ctx), graph=few(t)), 1))
+        us = timer.us(lambda: ops.moe_experts(x, ids, weights, w1, w3, w2, w13), graph=few(t))
         row["experts_us"] = round(us, 1)
         row["experts_tflops"] = round(6 * t * top * f * width / (us * 1e-6) / 1e12, 1)
         row["experts_tensor_frac"] = round(6 * t * top * f * width / (us * 1e-6) / tensor, 3)
@@ -614,7 +630,7 @@ def tanupel_kernel_table(size, device, peaks) -> Dict[str, dict]:
                 g = torch.empty(t, ffn, dtype=torch.bfloat16, device=device)
                 ops.silu_gate(ops.linear(x, wd13), g)
             return ops.linear(g, wd)
-        us = timer.us(dense)
+        us = timer.us(dense, graph=few(t))
         table[f"dense gated feed-forward t={t}: {ffn} rows (llama)"] = dict(
             us=round(us, 1), tflops=round(6 * t * ffn * width / (us * 1e-6) / 1e12, 1),
             tensor_frac=round(6 * t * ffn * width / (us * 1e-6) / tensor, 3),
