@@ -510,6 +510,9 @@ def test_decay_acts_per_head_and_key_channel(dtype):
     (5, 1, 16, 32, 0.2, 16, 1e4, (2.0,), 8.0, True),
     (2, 2, 80, 16, 0.11, 40, 2000.0, (2.0, 1.0, 8.0, 32), None, False),
     (3, 3, 24, 24, 0.3, None, 1.0, None, 2.0, False),                # no positions at all
+    (4, 2, 64, 64, 0.12, 32, 1e4, (2.0,), 3.0, True),                # capped, at the head sizes of the tcgen05 kernel
+    (2, 1, 128, 128, 0.09, 64, 1e4, (2.0,), 4.0, True),
+    (2, 2, 128, 64, 0.09, 128, 5e5, (4.0, 1.0, 4.0, 32), None, False),
 ])
 def test_attention_alone(dtype, sizes):
     """Queries and keys normed over the whole projection, a part of each head turned (dimension i
@@ -546,14 +549,15 @@ def test_attention_alone(dtype, sizes):
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("mode", ["prompt", "decoded"])
-def test_far_key_shows_through_the_cap(dtype, mode):
+@pytest.mark.parametrize("d", [16, 64])
+def test_far_key_shows_through_the_cap(dtype, mode, d):
     """One key 400 positions back has a score far above all others, through a dimension that is not
     turned.  Capped, it takes about half of the weight; uncapped it would take all of it, and
     without the key the output is another one: in a prompt portion and for tokens decoded alone,
     with the key on the first of many pages."""
     from fastgen_b200.config.tanupel import _attention
 
-    heads, kv, d, n, cap = 2, 1, 16, 420, 6.0
+    heads, kv, n, cap = 2, 1, 420, 6.0
     g = torch.Generator().manual_seed(21)
     m = _attn(heads, kv, d, d, 3.0, dims=8, base=1e4, scaling=(2.0,), softcap=cap)
 
