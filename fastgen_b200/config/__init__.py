@@ -16,6 +16,7 @@ from . import llama as _llama  # registers LlamaForCausalLM
 from . import sinorax as _sinorax  # registers Sinorax
 from . import zeladra as _zeladra  # registers Zeladra
 from . import tanupel as _tanupel  # registers Tanupel
+from . import palulorn as _palulorn  # registers Palulorn
 
 __all__ = [
     "ConfigError",

@@ -67,11 +67,14 @@ class ScheduleEntry:
     ``None`` gives the run a cache of its own.  ``step_row``: before this run, row ``step_row``
     of the model's table of step vectors (``ModelArgs.step_table_name``) is added to every token's
     residual stream (a run of layers that is passed several times marks each pass that way).
+    ``mix_input``: before this run (and before its step vector) the residual stream ``x`` becomes
+    ``W [x; x0]`` with ``x0`` the embedder's output and ``W`` the model's ``pass_input_name`` tensor.
     """
 
     layer: int
     kv_from: Optional[int] = None
     step_row: Optional[int] = None
+    mix_input: bool = False
 
 
 @dataclass(frozen=True)
@@ -103,9 +106,17 @@ class ModelArgs:
     #: (``ScheduleEntry.step_row``); ``None``: the model has none
     step_table_name: Optional[str] = None
     step_table_rows: int = 0
+    #: tensor [dim, 2 dim] that maps (stream, embedder's output) to the new stream before the
+    #: schedule entries marked ``mix_input``; ``None``: the model has none
+    pass_input_name: Optional[str] = None
 
     def __post_init__(self) -> None:
         n = len(self.layers)
+        if any(e.mix_input for e in self.schedule):
+            if self.pass_input_name is None:
+                raise ConfigError("a schedule entry mixes the embedder's output in, but the model names no tensor for it")
+            if self.streams is not None:
+                raise ConfigError("the embedder's output is mixed into one residual stream, not into several")
         for pos, entry in enumerate(self.schedule):
             if entry.step_row is not None:
                 if self.step_table_name is None or not 0 <= entry.step_row < self.step_table_rows:

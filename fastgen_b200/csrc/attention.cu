@@ -23,7 +23,8 @@ extern "C" int fg_attention_simt(const void* q, int q_stride, void* out, int out
                                  int table_width, int page_size, int n_pages, const int* pos,
                                  const int* tile_req, const int* tile_tok0, const int* tile_ntok,
                                  int n_tiles, int n_heads, int n_kv_heads, int head_dim, int window,
-                                 int keep_first, float scale, float softcap, int* status, cudaStream_t stream) {
+                                 int keep_first, float scale, float softcap, const float* sinks, int* status,
+                                 cudaStream_t stream) {
   using namespace fg_attn;
   if (n_tiles == 0) return 0;
   FG_CHECK_ARG(head_dim == FG_HEAD_DIM, "fg_attention_simt: library built for head size %d, got %d",
@@ -43,7 +44,7 @@ extern "C" int fg_attention_simt(const void* q, int q_stride, void* out, int out
     kern<<<grid, THREADS, smem, stream>>>((const float*)q, q_stride, (float*)out, out_stride,
                                           (const float*)k_pages, (const float*)v_pages, block_table,
                                           table_width, page_size, n_pages, pos, tile_req, tile_tok0,
-                                          tile_ntok, n_kv_heads, group, hpb, window, keep_first, scale, status, softcap);
+                                          tile_ntok, n_kv_heads, group, hpb, window, keep_first, scale, status, softcap, sinks);
   } else if (dtype == FG_BF16) {
     auto kern = attention_simt_kernel<__nv_bfloat16, FG_HEAD_DIM>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -52,7 +53,7 @@ extern "C" int fg_attention_simt(const void* q, int q_stride, void* out, int out
         (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride,
         (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table, table_width,
         page_size, n_pages, pos, tile_req, tile_tok0, tile_ntok, n_kv_heads, group, hpb, window, keep_first,
-        scale, status, softcap);
+        scale, status, softcap, sinks);
   } else {
     FG_CHECK_ARG(false, "fg_attention_simt: bad dtype %d", dtype);
   }
@@ -199,8 +200,8 @@ extern "C" int fg_attention_prefill_bf16(const void* q, int q_stride, void* out,
                                          int table_width, int page_size, int n_pages, const int* pos,
                                          const int* tile_req, const int* tile_tok0, const int* tile_ntok,
                                          int n_tiles, int n_heads, int n_kv_heads, int head_dim, int window,
-                                         int keep_first, float scale, float softcap, int* status,
-                                         cudaStream_t stream) {
+                                         int keep_first, float scale, float softcap, const float* sinks,
+                                         int* status, cudaStream_t stream) {
   using namespace fg_mma;
   if (n_tiles == 0) return 0;
   FG_CHECK_ARG(head_dim == FG_HEAD_DIM, "fg_attention_prefill_bf16: library built for head size %d, got %d",
@@ -225,7 +226,7 @@ extern "C" int fg_attention_prefill_bf16(const void* q, int q_stride, void* out,
       (const __nv_bfloat16*)v_pages, block_table, table_width, page_size, n_pages, pos, tile_req, tile_tok0,
       tile_ntok, n_kv_heads, group, hpb, window, scale * 1.4426950408889634f, status, nullptr, nullptr, nullptr,
       window > 0 ? keep_first : 0, softcap > 0.f ? softcap * 1.4426950408889634f : 0.f,
-      softcap > 0.f ? scale / softcap : 0.f);
+      softcap > 0.f ? scale / softcap : 0.f, sinks);
   FG_CHECK_LAUNCH("fg_attention_prefill_bf16");
   return 0;
 }
@@ -262,7 +263,7 @@ extern "C" int fg_attention_sigmoid_prefill_bf16(const void* q, int q_stride, vo
   kern<<<grid, THREADS, smem, stream>>>(
       (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pages,
       (const __nv_bfloat16*)v_pages, block_table, table_width, page_size, n_pages, pos, tile_req, tile_tok0,
-      tile_ntok, n_kv_heads, group, hpb, window, scale, status, gate, r1, r2, 0, 0.f, 0.f);
+      tile_ntok, n_kv_heads, group, hpb, window, scale, status, gate, r1, r2, 0, 0.f, 0.f, nullptr);
   FG_CHECK_LAUNCH("fg_attention_sigmoid_prefill_bf16");
   return 0;
 }
@@ -275,7 +276,8 @@ extern "C" int fg_attention_decode_bf16(const void* q, int q_stride, void* out, 
                                         const int* seq_req, const int* seq_tok, int n_seqs, int n_heads,
                                         int n_kv_heads, int head_dim, int window, int keep_first, float scale,
                                         float* scratch, long long scratch_floats, int max_splits,
-                                        const float* out_freqs, float softcap, int* status, cudaStream_t stream) {
+                                        const float* out_freqs, float softcap, const float* sinks, int* status,
+                                        cudaStream_t stream) {
   using namespace fg_mma;
   if (n_seqs == 0) return 0;
   FG_CHECK_ARG(head_dim == FG_HEAD_DIM, "fg_attention_decode_bf16: library built for head size %d, got %d",
@@ -311,7 +313,7 @@ extern "C" int fg_attention_decode_bf16(const void* q, int q_stride, void* out, 
   dim3 cgrid(n_heads, n_seqs);
   attention_combine_kernel<FG_HEAD_DIM><<<cgrid, COMBINE_THREADS, 0, stream>>>(
       scratch, (__nv_bfloat16*)out, out_stride, pos, seq_req, seq_tok, n_heads, window, max_splits, nullptr, status,
-      out_freqs, keep_first);
+      out_freqs, keep_first, sinks);
   FG_CHECK_LAUNCH("fg_attention_combine");
   return 0;
 }
@@ -333,7 +335,8 @@ extern "C" int fg_attention_decode_tma_bf16(const void* q, int q_stride, void* o
                                             const int* seq_tok, int n_seqs, int n_heads, int n_kv_heads,
                                             int head_dim, int window, float scale, float* scratch,
                                             long long scratch_floats, int max_splits, long long max_pairs,
-                                            const float* out_freqs, int* status, cudaStream_t stream) {
+                                            const float* out_freqs, const float* sinks, int* status,
+                                            cudaStream_t stream) {
   using namespace fg_tma;
   if (n_seqs == 0) return 0;
   FG_CHECK_ARG(head_dim == FG_HEAD_DIM, "fg_attention_decode_tma_bf16: library built for head size %d, got %d",
@@ -394,7 +397,7 @@ extern "C" int fg_attention_decode_tma_bf16(const void* q, int q_stride, void* o
   dim3 cgrid(n_heads, n_seqs);
   fg_launch_pdl(fg_mma::attention_combine_kernel<FG_HEAD_DIM>, cgrid, dim3(fg_mma::COMBINE_THREADS), 0, stream,
                 (const float*)partials, (__nv_bfloat16*)out, out_stride, pos, seq_req, seq_tok, n_heads, window,
-                max_splits, combine_pairs, status, out_freqs, 0);
+                max_splits, combine_pairs, status, out_freqs, 0, sinks);
   FG_CHECK_LAUNCH("fg_attention_combine");
   return 0;
 }

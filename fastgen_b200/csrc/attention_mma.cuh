@@ -233,7 +233,9 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
                          const int* __restrict__ tile_ntok, int n_kv_heads, int group, int heads_per_block,
                          int window, float scale_log2, int* status, const float* __restrict__ gate,
                          const float* __restrict__ dist_r1, const float* __restrict__ dist_r2, int keep_first,
-                         float cap_log2, float scale_by_cap) {
+                         float cap_log2, float scale_by_cap, const float* __restrict__ sinks) {
+  // sinks (softmax only): float32 per query head; exp(sink_h) joins the denominator once, without a
+  // key or a value: the running maximum and sum of a row start from it
   // keep_first (with a window): so many of the sequence's first positions stay visible to every
   // query; the key tiles that hold them are walked before the tiles of the window
   constexpr int LD = Tile<HD>::LD;
@@ -326,6 +328,14 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
 #pragma unroll
   for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  if (!SIGMOID && sinks != nullptr) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      if (!row_valid(h ? r1 : r0)) continue;
+      m[h] = sinks[g * group + row_head(h ? r1 : r0)] * 1.4426950408889634f;  // the softmax runs in base 2
+      l[h] = 1.f;
+    }
+  }
   // the heads' numbers of this thread's two rows (sigmoid weights only)
   float gate_r[2] = {0.f, 0.f}, r1_r[2] = {0.f, 0.f}, r2_r[2] = {0.f, 0.f};
   if (SIGMOID) {
@@ -620,7 +630,9 @@ attention_combine_kernel(const float* scratch, __nv_bfloat16* __restrict__ out, 
                          const int* __restrict__ pos, const int* __restrict__ seq_req,
                          const int* __restrict__ seq_tok, int n_heads, int window, int max_splits,
                          const int* first_pair, int* status, const float* __restrict__ out_freqs,
-                         int keep_first) {
+                         int keep_first, const float* __restrict__ sinks) {
+  // sinks: null, or float32 per query head: exp(sink_h) joins the denominator once (it has no key and
+  // no value, so no split holds it: it is added here, where the splits meet)
   // keep_first (with a window, partials numbered [request][head][split] only): the splits that
   // hold kept first positions are summed before those of the window
   // out_freqs: null, or HD/2 frequencies by which the output's adjacent pairs are turned
@@ -675,6 +687,8 @@ attention_combine_kernel(const float* scratch, __nv_bfloat16* __restrict__ out, 
   mm = red[0];
 #pragma unroll
   for (int w = 1; w < WARPS; ++w) mm = fmaxf(mm, red[w]);
+  const float sink2 = sinks != nullptr ? sinks[head] * 1.4426950408889634f : -INFINITY;  // base 2, as the partials
+  mm = fmaxf(mm, sink2);
   // this warp's splits
   float2 acc[NV];
 #pragma unroll
@@ -706,6 +720,7 @@ attention_combine_kernel(const float* scratch, __nv_bfloat16* __restrict__ out, 
   float total = 0.f;
 #pragma unroll
   for (int w = 0; w < WARPS; ++w) total += ll_s[w];
+  if (sinks != nullptr) total += exp2f(sink2 - mm);
   const float inv = total > 0.f ? 1.f / total : 0.f;
   if (out_freqs != nullptr) {
     for (int j = tid; j < HD / 2; j += COMBINE_THREADS) {

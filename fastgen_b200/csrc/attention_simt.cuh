@@ -12,7 +12,8 @@
 // Semantics of fastgen/forward.py:176-258: softmax(q.k * scale) v over the
 // positions j <= pos(query) of the query's own request (and, when a window is given,
 // j > pos - window or j < keep_first: the first positions stay visible), grouped-query heads h -> h / (Hq/Hkv).
-// Running maximum, sum and output accumulator are float32; exp is expf.
+// Running maximum, sum and output accumulator are float32; exp is expf.  With `sinks` (float32 per
+// query head) the denominator also holds exp(sink_h): a score without a key, unscaled, counted once.
 //
 // Storage type T (float or bf16) only affects loads and the final store.
 #pragma once
@@ -33,7 +34,7 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
                       int n_pages, const int* __restrict__ pos, const int* __restrict__ tile_req,
                       const int* __restrict__ tile_tok0, const int* __restrict__ tile_ntok,
                       int n_kv_heads, int group, int heads_per_block, int window, int keep_first,
-                      float scale, int* status, float softcap) {
+                      float scale, int* status, float softcap, const float* __restrict__ sinks) {
   constexpr int HP = HD + 1;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float(*Qs)[HP] = reinterpret_cast<float(*)[HP]>(smem_raw);
@@ -101,6 +102,12 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
   for (int i = 0; i < 4; ++i) {
     m_run[i] = -INFINITY;
     l_run[i] = 0.f;
+    // a sink: a learned score per query head that has no key and no value and counts once in the
+    // denominator; the running maximum and sum start from it
+    if (sinks != nullptr && row_head(warp + 4 * i) < group) {
+      m_run[i] = sinks[g * group + row_head(warp + 4 * i)];
+      l_run[i] = 1.f;
+    }
   }
   // this thread's output elements: row tid/8, columns tid%8 + 8*i
   constexpr int OD = HD / 8;

@@ -206,6 +206,12 @@ def delta_rule_library() -> ctypes.CDLL:
     return load("fg_delta", ["delta_rule.cu", "errors.cu"])
 
 
+def recurrent_library() -> ctypes.CDLL:
+    """The kernels of the matrix memory with exponential gates and of the gated linear recurrent unit
+    (compiled when a model with such a mixer is bound)."""
+    return load("fg_recur", ["mlstm.cu", "rglru.cu", "errors.cu"])
+
+
 def moe_library() -> ctypes.CDLL:
     """The kernels of the feed-forward with routed experts."""
     return load("fg_moe", ["moe.cu", "errors.cu"])
@@ -230,6 +236,7 @@ def build_all(head_dims: Sequence[int] = (16, 32, 64, 128), latent_sizes: Sequen
     _compile("fg_core", CORE_SOURCES)
     _compile("fg_delta", ["delta_rule.cu", "errors.cu"])
     _compile("fg_moe", ["moe.cu", "errors.cu"])
+    _compile("fg_recur", ["mlstm.cu", "rglru.cu", "errors.cu"])
     for rank, rot in latent_sizes:
         _compile(f"fg_latent_r{rank}_t{rot}", ["latent_mma.cu", "errors.cu"],
                  [f"FG_LATENT_RANK={rank}", f"FG_LATENT_ROT={rot}"])

@@ -36,11 +36,12 @@ constexpr int THREADS = WARPS * 32;
 
 enum { EPI_PLAIN = 0, EPI_QKV = 1, EPI_SWIGLU = 2 };
 
-enum { ACT_NONE = 0, ACT_GELU_ERF = 1, ACT_GELU_TANH = 2 };
+enum { ACT_NONE = 0, ACT_GELU_ERF = 1, ACT_GELU_TANH = 2, ACT_RELU2 = 3 };
 
 __device__ __forceinline__ float activate(float z, int act) {
   if (act == ACT_GELU_ERF) return 0.5f * z * (1.f + erff(z * 0.70710678118654752440f));
   if (act == ACT_GELU_TANH) return 0.5f * z * (1.f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+  if (act == ACT_RELU2) return z > 0.f ? z * z : 0.f;
   return z;
 }
 
@@ -403,7 +404,7 @@ extern "C" int fg_gemm_skinny_bf16(const void* x, int ldx, const void* w, int ld
                                    cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   if (check_common("fg_gemm_skinny_bf16", x, ldx, w, ldw, ldy, M, N, K, K)) return -1;
-  FG_CHECK_ARG(act >= ACT_NONE && act <= ACT_GELU_TANH, "fg_gemm_skinny_bf16: unknown activation %d", act);
+  FG_CHECK_ARG(act >= ACT_NONE && act <= ACT_RELU2, "fg_gemm_skinny_bf16: unknown activation %d", act);
   QkvEpilogue none{};
   none.bias = (const __nv_bfloat16*)bias;
   none.act = act;

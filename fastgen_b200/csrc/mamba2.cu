@@ -32,9 +32,10 @@ constexpr int CONV_MAX_TAPS = 8;
 // tokens ago), and neighbouring threads' re-reads hit the cache.
 constexpr int CONV_TOKENS = 4;
 
-template <typename T>
+// TO: the output's type; SILU: whether the sum passes SiLU (else it is stored as it is).
+template <typename T, typename TO, bool SILU>
 __global__ void __launch_bounds__(CONV_THREADS)
-conv_silu_kernel(const T* __restrict__ in, long in_stride, float* __restrict__ out, long out_stride,
+conv_silu_kernel(const T* __restrict__ in, long in_stride, TO* __restrict__ out, long out_stride,
                  const float* __restrict__ w, const float* __restrict__ bias, const float* __restrict__ state,
                  long state_stride, long conv_offset, const int* __restrict__ req, int n_tokens, int channels,
                  int taps) {
@@ -79,7 +80,7 @@ conv_silu_kernel(const T* __restrict__ in, long in_stride, float* __restrict__ o
 #pragma unroll
     for (int k = 0; k < CONV_MAX_TAPS; ++k)
       if (k < taps) acc = fmaf(wk[k], v[u][k], acc);
-    out[(size_t)(t0 + u) * out_stride + c] = acc / (1.f + expf(-acc));
+    out[(size_t)(t0 + u) * out_stride + c] = from_f32<TO>(SILU ? acc / (1.f + expf(-acc)) : acc);
   }
 }
 
@@ -447,37 +448,54 @@ gated_part_norm_warp_kernel(const float* __restrict__ y, long y_stride, const T*
 
 // ---- C interface -----------------------------------------------------------------------------------
 
+// A causal convolution over time per channel, from and into the state's last inputs, with a choice
+// of activation (act 1: SiLU, 0: none) and of the output's type (out_dtype).
+template <typename T, typename TO>
+static int launch_time_conv(const T* in, long proj_stride, TO* out, long out_stride, const float* w, const float* bias,
+                            float* state, long state_stride, long conv_offset, const int* req, const int* seq_slot,
+                            const int* seq_start, int n_tokens, int n_seqs, int channels, int taps, int act,
+                            cudaStream_t stream) {
+  const dim3 grid((n_tokens + CONV_TOKENS - 1) / CONV_TOKENS, (channels + CONV_THREADS - 1) / CONV_THREADS);
+  const dim3 sgrid(n_seqs, grid.y);
+  if (act)
+    conv_silu_kernel<T, TO, true><<<grid, CONV_THREADS, 0, stream>>>(in, proj_stride, out, out_stride, w, bias, state,
+                                                                     state_stride, conv_offset, req, n_tokens, channels,
+                                                                     taps);
+  else
+    conv_silu_kernel<T, TO, false><<<grid, CONV_THREADS, 0, stream>>>(in, proj_stride, out, out_stride, w, bias, state,
+                                                                      state_stride, conv_offset, req, n_tokens,
+                                                                      channels, taps);
+  FG_CHECK_LAUNCH("fg_time_conv");
+  if (taps > 1)
+    conv_state_kernel<T><<<sgrid, CONV_THREADS, 0, stream>>>(in, proj_stride, state, state_stride, conv_offset, seq_slot,
+                                                             seq_start, channels, taps);
+  FG_CHECK_LAUNCH("fg_time_conv (state)");
+  return 0;
+}
+
+extern "C" int fg_time_conv(const void* proj, long proj_stride, long offset, int dtype, void* out, long out_stride,
+                            int out_dtype, const float* w, const float* bias, float* state, long state_stride,
+                            long conv_offset, const int* req, const int* seq_slot, const int* seq_start, int n_tokens,
+                            int n_seqs, int channels, int taps, int act, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  FG_CHECK_ARG(taps >= 1 && taps <= CONV_MAX_TAPS, "fg_time_conv: %d taps (1 to %d)", taps, CONV_MAX_TAPS);
+  FG_CHECK_ARG((dtype == FG_F32 || dtype == FG_BF16) && (out_dtype == FG_F32 || out_dtype == dtype),
+               "fg_time_conv: types %d -> %d", dtype, out_dtype);
+#define FG_CONV_ARGS w, bias, state, state_stride, conv_offset, req, seq_slot, seq_start, n_tokens, n_seqs, channels, taps, act, stream
+  if (dtype == FG_F32)
+    return launch_time_conv((const float*)proj + offset, proj_stride, (float*)out, out_stride, FG_CONV_ARGS);
+  if (out_dtype == FG_F32)
+    return launch_time_conv((const __nv_bfloat16*)proj + offset, proj_stride, (float*)out, out_stride, FG_CONV_ARGS);
+  return launch_time_conv((const __nv_bfloat16*)proj + offset, proj_stride, (__nv_bfloat16*)out, out_stride, FG_CONV_ARGS);
+#undef FG_CONV_ARGS
+}
+
 extern "C" int fg_mamba2_conv(const void* proj, long proj_stride, long xbc_offset, int dtype, float* out,
                               long out_stride, const float* w, const float* bias, float* state, long state_stride,
                               long conv_offset, const int* req, const int* seq_slot, const int* seq_start,
                               int n_tokens, int n_seqs, int channels, int taps, cudaStream_t stream) {
-  if (n_tokens == 0) return 0;
-  FG_CHECK_ARG(taps >= 1 && taps <= CONV_MAX_TAPS, "fg_mamba2_conv: %d taps (1 to %d)", taps, CONV_MAX_TAPS);
-  const dim3 grid((n_tokens + CONV_TOKENS - 1) / CONV_TOKENS, (channels + CONV_THREADS - 1) / CONV_THREADS);
-  const dim3 sgrid(n_seqs, grid.y);
-  if (dtype == FG_F32) {
-    const float* in = (const float*)proj + xbc_offset;
-    conv_silu_kernel<float><<<grid, CONV_THREADS, 0, stream>>>(in, proj_stride, out, out_stride, w,
-                                                               bias, state, state_stride, conv_offset,
-                                                               req, n_tokens, channels, taps);
-    FG_CHECK_LAUNCH("fg_mamba2_conv");
-    if (taps > 1)
-      conv_state_kernel<float><<<sgrid, CONV_THREADS, 0, stream>>>(in, proj_stride, state, state_stride, conv_offset,
-                                                                   seq_slot, seq_start, channels, taps);
-  } else if (dtype == FG_BF16) {
-    const __nv_bfloat16* in = (const __nv_bfloat16*)proj + xbc_offset;
-    conv_silu_kernel<__nv_bfloat16><<<grid, CONV_THREADS, 0, stream>>>(
-        in, proj_stride, out, out_stride, w, bias, state, state_stride,
-        conv_offset, req, n_tokens, channels, taps);
-    FG_CHECK_LAUNCH("fg_mamba2_conv");
-    if (taps > 1)
-      conv_state_kernel<__nv_bfloat16><<<sgrid, CONV_THREADS, 0, stream>>>(
-          in, proj_stride, state, state_stride, conv_offset, seq_slot, seq_start, channels, taps);
-  } else {
-    FG_CHECK_ARG(false, "fg_mamba2_conv: bad dtype %d", dtype);
-  }
-  FG_CHECK_LAUNCH("fg_mamba2_conv (state)");
-  return 0;
+  return fg_time_conv(proj, proj_stride, xbc_offset, dtype, out, out_stride, FG_F32, w, bias, state, state_stride,
+                      conv_offset, req, seq_slot, seq_start, n_tokens, n_seqs, channels, taps, 1, stream);
 }
 
 template <typename T>

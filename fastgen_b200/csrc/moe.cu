@@ -206,6 +206,169 @@ extern "C" int fg_moe_route(const float* logits, const float* correction, int* i
   return 0;
 }
 
+// ---- choice among groups of experts, sigmoid scores ------------------------------------------------
+// kind 0: scores s = softmax(logits); kind 1: s = sigmoid(logits).  With n_groups > 0 the experts form
+// n_groups equal groups of neighbours; a group's score is the sum of its `group_top` largest scores, and
+// only experts of the `keep_groups` best groups (equal ones: the lower index) can be chosen.  The `top`
+// experts with the largest s + correction among those are chosen (equal ones: the lower index); their
+// weights are their s, divided with `renormalize` by (their sum + renorm_eps), then times weight_scale.
+// A warp a token; the scores pass through the warp's row of shared memory.
+constexpr int ROUTE_WARPS = 4;
+
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+moe_route_groups_kernel(const float* logits, const float* __restrict__ correction, int* __restrict__ ids,
+                        float* __restrict__ weights, const int* __restrict__ req, int n_tokens, int n_experts, int top,
+                        int kind, int n_groups, int keep_groups, int group_top, int renormalize, float renorm_eps,
+                        float weight_scale) {
+  __shared__ float s_s[ROUTE_WARPS][32 * ROUTE_MAX_PER_LANE];
+  __shared__ float g_s[ROUTE_WARPS][32 * ROUTE_MAX_PER_LANE];
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * ROUTE_WARPS + w;
+  if (t >= n_tokens) return;
+  if (req[t] < 0) {
+    for (int k = lane; k < top; k += 32) {
+      ids[(size_t)t * top + k] = -1;
+      weights[(size_t)t * top + k] = 0.f;
+    }
+    return;
+  }
+  float s[ROUTE_MAX_PER_LANE], c[ROUTE_MAX_PER_LANE];
+  if (kind == 0) {
+    float m = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
+      const int e = lane + 32 * i;
+      s[i] = e < n_experts ? logits[(size_t)t * n_experts + e] : -INFINITY;
+      m = fmaxf(m, s[i]);
+    }
+    m = warp_max(m);
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
+      s[i] = lane + 32 * i < n_experts ? expf(s[i] - m) : 0.f;
+      sum += s[i];
+    }
+    sum = warp_sum(sum);
+#pragma unroll
+    for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) s[i] = s[i] / sum;
+  } else {
+#pragma unroll
+    for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
+      const int e = lane + 32 * i;
+      s[i] = e < n_experts ? 1.f / (1.f + expf(-logits[(size_t)t * n_experts + e])) : 0.f;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
+    const int e = lane + 32 * i;
+    c[i] = e < n_experts ? s[i] + (correction ? correction[e] : 0.f) : -INFINITY;
+    if (e < n_experts) s_s[w][e] = s[i];
+  }
+  if (n_groups > 0) {
+    __syncwarp();
+    const int per = n_experts / n_groups;
+    // a group's score: its group_top largest scores added, largest first
+    for (int gi = lane; gi < n_groups; gi += 32) {
+      float total = 0.f;
+      float last = INFINITY;
+      int last_e = -1;
+      for (int k = 0; k < group_top && k < per; ++k) {
+        // the largest score below (last, last_e) in the order (score descending, index ascending)
+        float best = -INFINITY;
+        int best_e = -1;
+        for (int j = 0; j < per; ++j) {
+          const float v = s_s[w][gi * per + j];
+          const bool after = v < last || (v == last && j > last_e);
+          if (after && (v > best || best_e < 0)) {
+            best = v;
+            best_e = j;
+          }
+        }
+        if (best_e < 0) break;
+        total += best;
+        last = best;
+        last_e = best_e;
+      }
+      g_s[w][gi] = total;
+    }
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
+      const int e = lane + 32 * i;
+      if (e >= n_experts) continue;
+      const int gi = e / per;
+      const float mine = g_s[w][gi];
+      int rank = 0;  // groups ahead of this one
+      for (int o = 0; o < n_groups; ++o) {
+        const float v = g_s[w][o];
+        rank += (v > mine || (v == mine && o < gi)) ? 1 : 0;
+      }
+      if (rank >= keep_groups) c[i] = -INFINITY;
+    }
+  }
+  float total = 0.f;
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY, best_s = 0.f;
+    int best_e = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
+      const int e = lane + 32 * i;
+      if (e < n_experts && (c[i] > best || (c[i] == best && e < best_e))) {
+        best = c[i];
+        best_e = e;
+        best_s = s[i];
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      const float os = __shfl_xor_sync(0xffffffffu, best_s, o);
+      if (ob > best || (ob == best && oe < best_e)) {
+        best = ob;
+        best_e = oe;
+        best_s = os;
+      }
+    }
+    total += best_s;  // every lane holds the same sum, in ascending choice
+    if (lane == 0) {
+      ids[(size_t)t * top + k] = best_e;
+      weights[(size_t)t * top + k] = best_s;
+    }
+#pragma unroll
+    for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i)
+      if (lane + 32 * i == best_e) c[i] = -INFINITY;
+  }
+  __syncwarp();
+  if (renormalize || weight_scale != 1.f)
+    for (int k = lane; k < top; k += 32) {
+      const float wgt = weights[(size_t)t * top + k];
+      weights[(size_t)t * top + k] = (renormalize ? wgt / (total + renorm_eps) : wgt) * weight_scale;
+    }
+}
+
+extern "C" int fg_moe_route_groups(const float* logits, const float* correction, int* ids, float* weights,
+                                   const int* req, int n_tokens, int n_experts, int top, int kind, int n_groups,
+                                   int keep_groups, int group_top, int renormalize, float renorm_eps,
+                                   float weight_scale, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  FG_CHECK_ARG(n_experts >= 1 && n_experts <= 32 * ROUTE_MAX_PER_LANE, "fg_moe_route_groups: %d experts (1 to %d)",
+               n_experts, 32 * ROUTE_MAX_PER_LANE);
+  FG_CHECK_ARG(top >= 1 && top <= n_experts, "fg_moe_route_groups: %d of %d experts", top, n_experts);
+  FG_CHECK_ARG(kind == 0 || kind == 1, "fg_moe_route_groups: unknown kind of score %d", kind);
+  if (n_groups > 0) {
+    FG_CHECK_ARG(n_experts % n_groups == 0 && keep_groups >= 1 && keep_groups <= n_groups && group_top >= 1,
+                 "fg_moe_route_groups: %d experts in %d groups of which %d", n_experts, n_groups, keep_groups);
+    FG_CHECK_ARG(keep_groups * (n_experts / n_groups) >= top, "fg_moe_route_groups: %d groups cannot hold %d experts",
+                 keep_groups, top);
+  }
+  moe_route_groups_kernel<<<(n_tokens + ROUTE_WARPS - 1) / ROUTE_WARPS, ROUTE_WARPS * 32, 0, stream>>>(
+      logits, correction, ids, weights, req, n_tokens, n_experts, top, kind, n_groups, keep_groups, group_top,
+      renormalize, renorm_eps, weight_scale);
+  FG_CHECK_LAUNCH("fg_moe_route_groups");
+  return 0;
+}
+
 // ---- the plan -----------------------------------------------------------------------------------
 // One block.  A warp takes experts w, w + 32, ...: it walks all pairs 32 at a time and counts (first
 // pass) or places (second pass) those of its expert, in ascending pair order.

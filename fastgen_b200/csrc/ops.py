@@ -47,6 +47,9 @@ _CORE_SIGNATURES = {
     "fg_embedding": [_P, _I, _P, _P, _I, _I, _I, _I, _F, _I, _P, _P],
     "fg_stream_norm": [_P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _F, _I, _P],
     "fg_mamba2_conv": [_P, _L, _L, _I, _P, _L, _P, _P, _P, _L, _L, _P, _P, _P, _I, _I, _I, _I, _P],
+    "fg_time_conv": [_P, _L, _L, _I, _P, _L, _I, _P, _P, _P, _L, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "fg_head_gate": [_P, _L, _P, _L, _I, _P, _I, _I, _I, _P],
+    "fg_qk_head_factors": [_P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P, _P, _P, _I, _P],
     "fg_mamba2_scan": [_P, _L, _P, _L, _L, _I, _P, _P, _P, _P, _L, _P, _L, _P, _P, _I, _I, _I, _I, _I, _P],
     "fg_gated_part_norm": [_P, _L, _P, _L, _I, _P, _P, _L, _P, _I, _I, _I, _F, _P],
     "fg_rms_rows": [_P, _L, _I, _P, _F, _P, _L, _I, _I, _P],
@@ -61,7 +64,7 @@ _CORE_SIGNATURES = {
     "fg_bias_act": [_P, _P, _I, _I, _I, _I, _P],
     "fg_scale_softcap": [_P, _I, _I, _F, _F, _P],
     "fg_rope_kv_write": [_P, _I, _P, _I, _P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P,
-                         _P, _P],
+                         _P, _I, _P],
     "fg_qk_rstd": [_P, _L, _I, _I, _P, _L, _I, _I, _I, _P, _F, _P, _I, _P],
     "fg_rmsnorm_sum": [_P, _P, _P, _I, _I, _P, _P, _I, _I, _P, _I, _P, _I, _I, _F, _P],
     "fg_gemm_f32_nt_from": [_P, _I, _I, _P, _I, _P, _I, _I, _I, _I, _P],
@@ -78,7 +81,7 @@ _CORE_SIGNATURES = {
 
 _ATTN_SIGNATURES = {
     "fg_attention_simt": [_P, _I, _P, _I, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F,
-                          _P, _P],
+                          _P, _P, _P],
     "fg_attention_sigmoid": [_P, _I, _P, _I, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F,
                              _P, _P, _P, _P, _P],
     "fg_attention_sigmoid_prefill_tc5_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I,
@@ -88,16 +91,16 @@ _ATTN_SIGNATURES = {
     "fg_attention_sigmoid_prefill_bf16": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I,
                                           _F, _P, _P, _P, _P, _P],
     "fg_attention_prefill_bf16": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F,
-                                  _P, _P],
+                                  _P, _P, _P],
     "fg_attention_decode_bf16": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P,
-                                 ctypes.c_longlong, _I, _P, _F, _P, _P],
+                                 ctypes.c_longlong, _I, _P, _F, _P, _P, _P],
     "fg_attention_prefill_tma_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I,
                                       _I, _F, _I, _P, _P],
     "fg_attention_prefill_tc5_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I,
                                       _I, _F, _P, _P, _P, _I, _I, _P, _I, _F, _P, _P],
     "fg_attention_prefill_tc5_split_slots": [_I, _I, _I, _I, _I],
     "fg_attention_decode_tma_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I,
-                                     _F, _P, ctypes.c_longlong, _I, ctypes.c_longlong, _P, _P, _P],
+                                     _F, _P, ctypes.c_longlong, _I, ctypes.c_longlong, _P, _P, _P, _P],
     "fg_attention_decode_is_persistent": [_I, _I, _I, _I],
 }
 
@@ -110,7 +113,7 @@ DECODE_SPLIT = 128   # key positions per split of the bfloat16 single-token kern
 SIGMOID_DECODE_KEYS = 256  # key positions per stretch of the sigmoid attention's single-token kernel
 
 #: activations the products' epilogues and ``bias_act`` know
-ACTIVATIONS = {None: 0, "none": 0, "gelu_erf": 1, "gelu_tanh": 2}
+ACTIVATIONS = {None: 0, "none": 0, "gelu_erf": 1, "gelu_tanh": 2, "relu2": 3}
 
 
 def _declare(lib: ctypes.CDLL, signatures) -> None:
@@ -189,14 +192,35 @@ _DELTA_SIGNATURES = {
 _MOE_SIGNATURES = {
     "fg_moe_logits": [_P, _I, _L, _P, _L, _P, _P, _I, _I, _I, _P],
     "fg_moe_route": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+    "fg_moe_route_groups": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _P],
     "fg_moe_plan": [_P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P, _P],
     "fg_moe_gather": [_P, _L, _P, _L, _I, _P, _P, _I, _I, _I, _I, _P],
     "fg_moe_gemm": [_P, _L, _P, _P, _L, _P, _L, _I, _I, _I, _P, _I, _P, _P, _P, _P, _I, _P],
     "fg_moe_gemm_mma": [_P, _L, _P, _P, _L, _P, _L, _I, _I, _P, _I, _P, _P, _P, _P, _I, _P],
     "fg_moe_combine": [_P, _L, _P, _P, _P, _L, _I, _I, _I, _I, _P],
 }
+_RECUR_SIGNATURES = {
+    "fg_mlstm_scan": [_P, _P, _F, _P, _L, _P, _L, _P, _L, _I, _P, _P, _L, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _F,
+                      _P],
+    "fg_mlstm_out": [_P, _L, _P, _P, _L, _I, _P, _P, _L, _P, _I, _I, _I, _F, _P],
+    "fg_rglru_scan": [_P, _I, _P, _L, _I, _P, _P, _P, _P, _P, _L, _P, _L, _I, _P, _L, _L, _P, _P, _P, _I, _I, _I, _I,
+                      _P],
+}
 _delta = None
 _moe = None
+_recur = None
+
+
+def recurrent():
+    """The library of the matrix memory with exponential gates and of the gated linear recurrent unit."""
+    global _recur
+    if _recur is None:
+        lib = build.recurrent_library()
+        _declare(lib, _RECUR_SIGNATURES)
+        lib.fg_mlstm_state_floats.argtypes = [_I, _I, _I]
+        lib.fg_mlstm_state_floats.restype = ctypes.c_longlong
+        _recur = lib
+    return _recur
 
 
 def delta_rule():
@@ -599,7 +623,8 @@ class Ops:
         """``h += row + sum_i coef_i * delta_i`` (float32), then ``out = rmsnorm(h) * weight`` (times
         ``1 + weight`` with ``one_plus``).  ``terms`` is a sequence of ``(delta [T, dim], coef)`` of one
         dtype (at most four); ``row`` a float32 [dim] vector or ``None``.  With ``out=None`` only the sum
-        is done; with ``rows`` only those rows are summed and normed and ``h`` stays as it was."""
+        is done; with ``rows`` only those rows are summed and normed and ``h`` stays as it was.  With ``out``
+        and no ``weight`` the summed rows are stored in ``out`` as they are (no norm)."""
         assert h.is_contiguous() and h.dtype == torch.float32
         dim = h.shape[1]
         n = h.shape[0] if rows is None else rows.numel()
@@ -611,7 +636,7 @@ class Ops:
         if row is not None:
             assert row.dtype == torch.float32 and row.is_contiguous() and row.numel() == dim
         if out is not None:
-            assert out.is_contiguous() and out.shape == (n, dim) and weight is not None and weight.is_contiguous()
+            assert out.is_contiguous() and out.shape == (n, dim) and (weight is None or weight.is_contiguous())
         assert rows is None or (rows.dtype == torch.int32 and out is not None)
         ptrs = (c_void_p * max(1, len(terms)))(*[d.data_ptr() for d, _ in terms])
         coefs = (c_float * max(1, len(terms)))(*[float(c) for _, c in terms])
@@ -692,10 +717,14 @@ class Ops:
                                       _ptr(ctx.req) if ctx is not None else None, t, n, k, _stream()))
         return out
 
-    def moe_route(self, logits, correction, top: int, ctx, renormalize: bool = False):
-        """Softmax over the experts (float32), choice of the ``top`` largest ``score + correction``
-        (equal ones: the lower index), weights = the chosen experts' scores (with ``renormalize``:
-        divided by their sum).  Returns (ids int32
+    def moe_route(self, logits, correction, top: int, ctx, renormalize: bool = False, score: str = "softmax",
+                  groups=None, renorm_eps: float = 0.0, weight_scale: float = 1.0):
+        """Scores over the experts (float32; ``score``: ``"softmax"`` or ``"sigmoid"``), choice of the
+        ``top`` largest ``score + correction`` (equal ones: the lower index), weights = the chosen
+        experts' scores (with ``renormalize``: divided by their sum plus ``renorm_eps``), times
+        ``weight_scale``.  ``groups = (count, keep, group_top)``: the experts form ``count`` equal groups of
+        neighbours, a group's score is the sum of its ``group_top`` largest scores, and only experts of
+        the ``keep`` best groups can be chosen.  Returns (ids int32
         [T, top], weights float32 [T, top]); padding tokens get expert -1."""
         lib = moe()
         t, n = logits.shape
@@ -703,11 +732,18 @@ class Ops:
         assert correction is None or (correction.dtype == torch.float32 and correction.numel() == n)
         ids = torch.empty((t, top), dtype=torch.int32, device=logits.device)
         weights = torch.empty((t, top), dtype=torch.float32, device=logits.device)
+        if score != "softmax" or groups is not None or renorm_eps or weight_scale != 1.0:
+            count, keep, group_top = groups if groups is not None else (0, 0, 0)
+            _check(lib, lib.fg_moe_route_groups(
+                _ptr(logits), _ptr(correction), _ptr(ids), _ptr(weights), _ptr(ctx.req), t, n, int(top),
+                {"softmax": 0, "sigmoid": 1}[score], int(count), int(keep), int(group_top), int(renormalize),
+                float(renorm_eps), float(weight_scale), _stream()))
+            return ids, weights
         _check(lib, lib.fg_moe_route(_ptr(logits), _ptr(correction), _ptr(ids), _ptr(weights), _ptr(ctx.req), t, n,
                                      int(top), int(renormalize), _stream()))
         return ids, weights
 
-    def moe_experts(self, x, ids, weights, w1, w3, w2, w13=None) -> torch.Tensor:
+    def moe_experts(self, x, ids, weights, w1, w3, w2, w13=None, act: Optional[str] = None) -> torch.Tensor:
         """``sum_k weights[t, k] * expert_{ids[t, k]}(x[t])`` with expert ``e`` the gated feed-forward
         ``w2[e] (silu(w1[e] x) * (w3[e] x))``; ``w1``, ``w3`` [E, F, K] (each expert's matrix contiguous,
         the experts a fixed stride apart: they may be the halves of ``w13`` [E, 2F, K]) and ``w2``
@@ -716,20 +752,26 @@ class Ops:
         allow, else (and in float32) with float32 sums in ascending order.  Many pairs in bfloat16 (a
         prompt portion), given ``w13``: the sorted rows are gathered and the two products are the
         vendor library's grouped product over the experts' row ranges, as a dense layer's large
-        products are the vendor's; gate and combine stay these kernels."""
+        products are the vendor's; gate and combine stay these kernels.
+
+        ``w3 = None``: the experts have no gate, ``w2[e] act(w1[e] x)`` with ``act`` a key of
+        ``ACTIVATIONS`` (``w13`` is then ``w1`` itself, for the grouped product)."""
         lib = moe()
         t, k = x.shape
         n_experts, f, _ = w1.shape
         top = ids.shape[1]
         pairs = t * top
-        assert x.stride(1) == 1 and w2.is_contiguous() and w1.stride() == w3.stride() and w1.stride(1) == k
-        assert w1.shape == w3.shape and w2.shape == (n_experts, k, f) and w1.dtype == x.dtype == w2.dtype
+        gated = w3 is not None
+        assert x.stride(1) == 1 and w2.is_contiguous() and w1.stride(1) == k
+        assert w2.shape == (n_experts, k, f) and w1.dtype == x.dtype == w2.dtype
+        assert not gated or (w1.shape == w3.shape and w1.stride() == w3.stride())
+        assert gated or ACTIVATIONS[act] >= 0
         w_stride = w1.stride(0)
         grouped = (w13 is not None and x.dtype == torch.bfloat16 and pairs >= MOE_GROUPED_PAIRS and k % 8 == 0
                    and f % 8 == 0 and hasattr(torch, "_grouped_mm") and not os.environ.get("FG_NO_GROUPED_MM"))
         mma = (not grouped and x.dtype == torch.bfloat16 and k % 8 == 0 and f % 8 == 0 and x.stride(0) % 8 == 0
-               and w_stride % 8 == 0 and x.data_ptr() % 16 == 0 and w1.data_ptr() % 16 == 0 and w3.data_ptr() % 16 == 0
-               and hasattr(lib, "fg_moe_gemm_mma") and not os.environ.get("FG_NO_MOE_MMA"))
+               and w_stride % 8 == 0 and x.data_ptr() % 16 == 0 and w1.data_ptr() % 16 == 0
+               and (not gated or w3.data_ptr() % 16 == 0) and hasattr(lib, "fg_moe_gemm_mma") and not os.environ.get("FG_NO_MOE_MMA"))
         tile_rows = lib.fg_moe_mma_tile_rows() if mma else lib.fg_moe_gemm_tile_rows()
         max_tiles = -(-pairs // tile_rows) + n_experts - 1
         plan = torch.empty(2 * pairs + 3 * max_tiles + 1 + n_experts, dtype=torch.int32, device=x.device)
@@ -748,23 +790,31 @@ class Ops:
                                           _ptr(expert_end), n_experts, top, pairs, k, _stream()))
             # rows beyond the last expert's end are never written and never read by the combine
             h = torch._grouped_mm(xs, w13.transpose(1, 2), offs=expert_end)
-            act = torch.empty((pairs, f), dtype=x.dtype, device=x.device)
-            self.silu_gate(h, act, 0)
-            y = torch._grouped_mm(act, w2.transpose(1, 2), offs=expert_end)
+            if gated:
+                mid = torch.empty((pairs, f), dtype=x.dtype, device=x.device)
+                self.silu_gate(h, mid, 0)
+            else:
+                mid = self.bias_act(h, act)
+            y = torch._grouped_mm(mid, w2.transpose(1, 2), offs=expert_end)
         else:
-            act = torch.empty((pairs, f), dtype=x.dtype, device=x.device)
+            # (rows beyond the plan's last tile are never written; zeroed where a kernel reads them all)
+            mid = (torch.empty if gated else torch.zeros)((pairs, f), dtype=x.dtype, device=x.device)
             y = torch.empty((pairs, k), dtype=x.dtype, device=x.device)
             tiles = (_ptr(tile_expert), _ptr(tile_row0), _ptr(tile_n), _ptr(n_tiles), max_tiles, _stream())
             if mma:
-                _check(lib, lib.fg_moe_gemm_mma(_ptr(x), x.stride(0), _ptr(w1), _ptr(w3), w_stride, _ptr(act),
-                                                act.stride(0), f, k, _ptr(row_pair), top, *tiles))
-                _check(lib, lib.fg_moe_gemm_mma(_ptr(act), act.stride(0), _ptr(w2), None, w2.stride(0), _ptr(y),
+                _check(lib, lib.fg_moe_gemm_mma(_ptr(x), x.stride(0), _ptr(w1), _ptr(w3), w_stride, _ptr(mid),
+                                                mid.stride(0), f, k, _ptr(row_pair), top, *tiles))
+                if not gated:
+                    self.bias_act(mid, act)
+                _check(lib, lib.fg_moe_gemm_mma(_ptr(mid), mid.stride(0), _ptr(w2), None, w2.stride(0), _ptr(y),
                                                 y.stride(0), k, f, None, top, *tiles))
             else:
                 code = _code(x.dtype)
-                _check(lib, lib.fg_moe_gemm(_ptr(x), x.stride(0), _ptr(w1), _ptr(w3), w_stride, _ptr(act), act.stride(0),
+                _check(lib, lib.fg_moe_gemm(_ptr(x), x.stride(0), _ptr(w1), _ptr(w3), w_stride, _ptr(mid), mid.stride(0),
                                             code, f, k, _ptr(row_pair), top, *tiles))
-                _check(lib, lib.fg_moe_gemm(_ptr(act), act.stride(0), _ptr(w2), None, w2.stride(0), _ptr(y), y.stride(0),
+                if not gated:
+                    self.bias_act(mid, act)
+                _check(lib, lib.fg_moe_gemm(_ptr(mid), mid.stride(0), _ptr(w2), None, w2.stride(0), _ptr(y), y.stride(0),
                                             code, k, f, None, top, *tiles))
         out = torch.empty((t, k), dtype=x.dtype, device=x.device)
         _check(lib, lib.fg_moe_combine(_ptr(y), y.stride(0), _ptr(weights), _ptr(pair_row), _ptr(out), out.stride(0),
@@ -876,12 +926,17 @@ class Ops:
         ``q``/``k``/``v`` are row-strided views [T, heads*head_dim]; ``k``/``v``
         may both be ``None`` (queries only).  ``qk_norm`` = (rstd [T, 2], query weights, key
         weights), all float32: queries and keys are multiplied by their token's factor (see
-        ``qk_rstd``) and their weights before they turn."""
+        ``qk_rstd``) and their weights before they turn.  An ``rstd`` of [T, heads + kv heads] holds a
+        factor per head instead (see ``qk_head_factors``); the weights may then be ``None`` (ones)."""
         rstd, qn_w, kn_w = qk_norm if qk_norm is not None else (None, None, None)
+        rstd_heads = 0
         if rstd is not None:
-            assert rstd.dtype == torch.float32 and rstd.is_contiguous() and rstd.shape == (q.shape[0], 2)
-            assert qn_w.dtype == torch.float32 and qn_w.numel() == n_heads * head_dim and qn_w.is_contiguous()
-            assert k is None or (kn_w.dtype == torch.float32 and kn_w.numel() == n_kv_heads * head_dim)
+            assert rstd.dtype == torch.float32 and rstd.is_contiguous() and rstd.shape[0] == q.shape[0]
+            # (with one query head and one key head the two layouts are the same)
+            rstd_heads = 0 if rstd.shape[1] == 2 else rstd.shape[1]
+            assert rstd_heads in (0, n_heads + n_kv_heads)
+            assert qn_w is None or (qn_w.dtype == torch.float32 and qn_w.numel() == n_heads * head_dim and qn_w.is_contiguous())
+            assert k is None or kn_w is None or (kn_w.dtype == torch.float32 and kn_w.numel() == n_kv_heads * head_dim)
         t = q.shape[0]
         assert q.stride(1) == 1 and pos.dtype == torch.int32 and req.dtype == torch.int32
         if k is not None:
@@ -898,7 +953,135 @@ class Ops:
             _ptr(freqs), _ptr(v_freqs) if k is not None else None, _ptr(k_pages) if k is not None else None,
             _ptr(v_pages) if k is not None else None,
             _ptr(block_table) if k is not None else None, width, page_size, n_pages,
-            t, n_heads, n_kv_heads, head_dim, _ptr(self.status), _ptr(rstd), _ptr(qn_w), _ptr(kn_w), _stream()))
+            t, n_heads, n_kv_heads, head_dim, _ptr(self.status), _ptr(rstd), _ptr(qn_w), _ptr(kn_w), rstd_heads,
+            _stream()))
+
+    def qk_head_factors(self, q, k, pos, req, n_heads: int, n_kv_heads: int, head_dim: int, real_dim: int,
+                        norm_eps: Optional[float] = None, temp=None) -> torch.Tensor:
+        """Per-head factors of queries and keys, float32 [T, heads + kv heads]: with ``norm_eps`` a
+        head's ``rsqrt(mean(x^2) + eps)`` over its first ``real_dim`` columns (an RMS norm per head; the
+        columns up to ``head_dim`` are padding and hold zeros); with ``temp = (coef, every)`` a query
+        head's factor is also multiplied by ``1 + coef * ln(floor((pos + 1) / every) + 1)``.  ``q`` /
+        ``k`` are row-strided views."""
+        t = q.shape[0]
+        assert q.stride(1) == 1 and k.stride(1) == 1 and k.dtype == q.dtype
+        coef, every = temp if temp is not None else (0.0, 0)
+        out = torch.empty((t, n_heads + n_kv_heads), dtype=torch.float32, device=q.device)
+        _check(self.lib, self.lib.fg_qk_head_factors(
+            _ptr(q), q.stride(0), _ptr(k), k.stride(0), _code(q.dtype), n_heads, n_kv_heads, head_dim, real_dim,
+            int(norm_eps is not None), float(norm_eps or 0.0), float(coef), int(every), _ptr(pos), _ptr(req), _ptr(out),
+            t, _stream()))
+        return out
+
+    def head_gate(self, x, gate, req, heads: int, head_dim: int) -> torch.Tensor:
+        """``x[t, h, :] *= sigmoid(gate[t, h])`` in place (float32 arithmetic): ``x`` [T, heads * head_dim],
+        ``gate`` a row-strided view [T, heads] of the same type."""
+        assert x.stride(1) == 1 and gate.stride(1) == 1 and x.dtype == gate.dtype and x.shape[1] == heads * head_dim
+        _check(self.lib, self.lib.fg_head_gate(_ptr(x), x.stride(0), _ptr(gate), gate.stride(0), _code(x.dtype),
+                                               _ptr(req), x.shape[0], heads, head_dim, _stream()))
+        return x
+
+    def time_conv(self, proj, offset: int, channels: int, weight, bias, state, conv_offset: int, taps: int, ctx,
+                  act: Optional[str] = None, out_dtype=None) -> torch.Tensor:
+        """Causal convolution over time per channel over the columns ``offset .. + channels`` of ``proj``
+        [T, .] (the last tap meets the current token; zeros before a sequence's start).  The inputs before
+        the step's tokens come from ``state`` [slots, .] (float32, ``taps - 1`` rows of ``channels`` from
+        ``conv_offset``), which is advanced.  ``act``: ``None`` or ``"silu"``; the result [T, channels] is
+        float32 or, with ``out_dtype``, of ``proj``'s type."""
+        t = proj.shape[0]
+        assert proj.stride(1) == 1 and state.dtype == torch.float32 and state.is_contiguous()
+        assert weight.dtype == torch.float32 and weight.shape == (channels, taps) and weight.is_contiguous()
+        assert act in (None, "silu") and out_dtype in (None, torch.float32, proj.dtype)
+        out = torch.empty((t, channels), dtype=out_dtype or torch.float32, device=proj.device)
+        _check(self.lib, self.lib.fg_time_conv(
+            _ptr(proj), proj.stride(0), int(offset), _code(proj.dtype), _ptr(out), out.stride(0), _code(out.dtype),
+            _ptr(weight), _ptr(bias), _ptr(state), state.stride(0), int(conv_offset), _ptr(ctx.req), _ptr(ctx.seq_slot),
+            _ptr(ctx.seq_start), t, ctx.n_seqs, channels, taps, int(act == "silu"), _stream()))
+        Ops.launches += int(taps > 1)
+        return out
+
+    # -- the matrix memory with exponential gates ------------------------------------------------------
+    def mlstm_state_floats(self, heads: int, d: int, dv: int) -> int:
+        return int(recurrent().fg_mlstm_state_floats(heads, d, dv))
+
+    def mlstm_scan(self, gates, gate_bias, cap: float, q, k, v, state, ctx, heads: int, d: int, dv: int,
+                   q_scale: float):
+        """The matrix memory per (sequence, head), token by token in float32, from and into ``state``
+        [slots, .] (``[heads][dv + 1][d]``, column ``dv`` being n, then the heads' running maxima):
+        ``m' = max(f + m, i); S <- exp(f + m - m') S + exp(i - m') k v^T`` and n likewise with k alone, with
+        ``i = cap tanh((gates_i + bias) / cap)``, ``f = logsigmoid(cap tanh((gates_f + bias) / cap))``.
+        ``gates`` float32 [T, 2 heads] raw sums (overwritten); ``q``, ``k`` [T, heads * d] and ``v``
+        [T, heads * dv] row-strided views of the compute type; q is multiplied by ``q_scale``.  Returns
+        ``(y, coef)``: y float32 [T, heads * (dv + 1)] (a head's ``S^T q``, then ``n . q``) and the
+        tokens' log coefficients [T, heads, 3] whose last is ``-m'``."""
+        lib = recurrent()
+        t = q.shape[0]
+        assert gates.dtype == torch.float32 and gates.is_contiguous() and gates.shape == (t, 2 * heads)
+        assert gate_bias.dtype == torch.float32 and gate_bias.numel() == 2 * heads and gate_bias.is_contiguous()
+        assert q.stride(1) == 1 and k.stride(1) == 1 and v.stride(1) == 1 and q.dtype == k.dtype == v.dtype
+        assert q.shape[1] == heads * d and k.shape[1] == heads * d and v.shape[1] == heads * dv
+        assert state.dtype == torch.float32 and state.is_contiguous()
+        coef = torch.empty((t, heads, 3), dtype=torch.float32, device=q.device)
+        y = torch.empty((t, heads * (dv + 1)), dtype=torch.float32, device=q.device)
+        _check(lib, lib.fg_mlstm_scan(
+            _ptr(gates), _ptr(gate_bias), float(cap), _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0),
+            _code(q.dtype), _ptr(coef), _ptr(y), y.stride(0), _ptr(state), state.stride(0), _ptr(ctx.req),
+            _ptr(ctx.seq_slot), _ptr(ctx.seq_start), t, ctx.n_seqs, heads, d, dv, float(q_scale), _stream()))
+        Ops.launches += 2  # the gates and the chain of running maxima
+        return y, coef
+
+    def mlstm_out(self, y, coef, z, weight, heads: int, dv: int, eps: float, ctx) -> torch.Tensor:
+        """``o = y / (max(|n . q|, exp(-m')) + 1e-6)`` per head, divided by its root mean square (``eps``),
+        times ``weight`` [heads * dv] and ``sigmoid(z)``; ``z`` a row-strided view of the compute type,
+        which the result has."""
+        lib = recurrent()
+        t = y.shape[0]
+        assert y.dtype == torch.float32 and y.stride(1) == 1 and z.stride(1) == 1 and z.shape == (t, heads * dv)
+        assert weight.dtype == torch.float32 and weight.numel() == heads * dv and weight.is_contiguous()
+        out = torch.empty((t, heads * dv), dtype=z.dtype, device=y.device)
+        _check(lib, lib.fg_mlstm_out(_ptr(y), y.stride(0), _ptr(coef), _ptr(z), z.stride(0), _code(z.dtype),
+                                     _ptr(weight), _ptr(out), out.stride(0), _ptr(ctx.req), t, heads, dv, float(eps),
+                                     _stream()))
+        return out
+
+    # -- the gated linear recurrent unit ---------------------------------------------------------------
+    def rglru_scan(self, gates, u, bias_r, bias_i, neg_rate, y, state, state_offset: int, ctx, blocks: int):
+        """``S <- a S + sqrt(1 - a^2) i u; out = S y`` per (sequence, channel), token by token in float32,
+        with ``r = sigmoid(gates_r + bias_r)``, ``i = sigmoid(gates_i + bias_i)``, ``a = exp(neg_rate r)``.
+        ``gates`` [blocks, T, 2 bw] (a block's r sums, then its i sums), ``u`` and ``y`` [T, width]
+        row-strided; ``state`` [slots, .] float32 holds S at ``state_offset``.  The result has ``y``'s
+        type."""
+        lib = recurrent()
+        t, width = y.shape
+        bw = width // blocks
+        assert gates.is_contiguous() and gates.shape == (blocks, t, 2 * bw)
+        assert u.stride(1) == 1 and y.stride(1) == 1 and u.shape == (t, width)
+        for vec in (bias_r, bias_i, neg_rate):
+            assert vec.dtype == torch.float32 and vec.numel() == width and vec.is_contiguous()
+        assert state.dtype == torch.float32 and state.is_contiguous()
+        coef = torch.empty((t, 2, width), dtype=torch.float32, device=y.device)
+        out = torch.empty((t, width), dtype=y.dtype, device=y.device)
+        _check(lib, lib.fg_rglru_scan(
+            _ptr(gates), _code(gates.dtype), _ptr(u), u.stride(0), _code(u.dtype), _ptr(bias_r), _ptr(bias_i),
+            _ptr(neg_rate), _ptr(coef), _ptr(y), y.stride(0), _ptr(out), out.stride(0), _code(y.dtype), _ptr(state),
+            state.stride(0), int(state_offset), _ptr(ctx.req), _ptr(ctx.seq_slot), _ptr(ctx.seq_start), t, ctx.n_seqs,
+            width, blocks, _stream()))
+        Ops.launches += 1  # the coefficients' kernel
+        return out
+
+    def block_products(self, x, w_t, w) -> torch.Tensor:
+        """A block-diagonal map: ``out[b] = x[:, b, :] @ w[b].T`` for ``x`` [T, blocks, a] (a strided
+        view), ``w`` [blocks, n, a]; returns float32 [blocks, T, n].  bfloat16 inputs go through the
+        library's batched product with float32 results (``w_t`` [blocks, a, n]); float32 runs this
+        package's float32 product block by block."""
+        t, blocks, a = x.shape
+        n = w.shape[1]
+        if x.dtype == torch.bfloat16:
+            return torch.bmm(x.permute(1, 0, 2), w_t, out_dtype=torch.float32)
+        out = torch.empty((blocks, t, n), dtype=torch.float32, device=x.device)
+        for b in range(blocks):
+            self.linear(x[:, b, :], w[b], out=out[b])
+        return out
 
     def qk_rstd(self, q, k, count_q: int, count_k: int, eps: float, req) -> torch.Tensor:
         """For every token the factors of an RMS norm over its whole query projection and over its
@@ -960,7 +1143,8 @@ class Ops:
 
     def attention(self, q, out, memory, ctx, n_heads: int, n_kv_heads: int, head_dim: int,
                   window: Optional[int], scale: float, out_freqs: Optional[torch.Tensor] = None,
-                  keep_first: int = 0, softcap: Optional[float] = None) -> bool:
+                  keep_first: int = 0, softcap: Optional[float] = None,
+                  sinks: Optional[torch.Tensor] = None) -> bool:
         """Paged causal attention of the step's query tokens; ``memory`` is the
         run's :class:`~fastgen_b200.cache.LayerMemory`, ``ctx`` the step's
         context.  bfloat16 runs on the tensor cores: prompt portions in one
@@ -972,8 +1156,12 @@ class Ops:
         every token of the step (a bfloat16 step of single tokens only: the merge of the splits
         turns what it stores), ``False`` if the caller still has to (``rotate_heads``).
 
-        ``softcap``: a scaled score ``s`` enters the softmax as ``softcap * tanh(s / softcap)``."""
+        ``softcap``: a scaled score ``s`` enters the softmax as ``softcap * tanh(s / softcap)``.
+
+        ``sinks`` (float32 [heads] or ``None``): ``exp(sinks[h])`` joins the softmax's denominator of head
+        ``h`` once; it has no key and no value and is not scaled."""
         lib = attn(head_dim)
+        assert sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == n_heads and sinks.is_contiguous())
         k_pages, v_pages, block_table, page_size = (
             memory.k_pages, memory.v_pages, memory.block_table, memory.page_size)
         assert q.stride(1) == 1 and out.stride(1) == 1
@@ -986,19 +1174,23 @@ class Ops:
                 _ptr(q), q.stride(0), _ptr(out), out.stride(0), _code(q.dtype), *common,
                 _ptr(tiles.req), _ptr(tiles.tok0), _ptr(tiles.ntok), tiles.n,
                 n_heads, n_kv_heads, head_dim, int(window or 0), keep_first, float(scale), float(softcap or 0.0),
-                _ptr(self.status), _stream()))
+                _ptr(sinks), _ptr(self.status), _stream()))
             return False
         # windows that keep a sequence's first positions visible run on the mma.sync kernels (on TMA
         # tiles for prompts where the pools have tensor maps), which walk the tiles of the kept
         # positions before those of the window
         # capped scores: the cap lives in the tcgen05 kernel (head sizes 64 and 128) and in the
         # mma.sync kernels on cp.async tiles
+        # sinks: prompt portions run on the mma.sync kernel on cp.async tiles, whose rows start their
+        # running maximum and sum from the sink; single tokens keep their kernels (the sink joins where
+        # the splits are merged)
         tc5 = head_dim in (64, 128) and self.use_tcgen05 and not keep_first
         use_tma = memory.tensor_maps is not None and (not softcap or tc5)
-        rows = PREFILL_TMA_ROWS if use_tma else PREFILL_ROWS
+        prompt_tma = use_tma and sinks is None
+        rows = PREFILL_TMA_ROWS if prompt_tma else PREFILL_ROWS
         tiling = attention_tiling(n_heads, n_kv_heads, rows)
         tiles = ctx.attention_tiles(tiling, 2)
-        if tiles.n and use_tma:
+        if tiles.n and prompt_tma:
             # head sizes 64 and 128: tcgen05.mma with S and O in tensor memory; other
             # multiples of 64: mma.sync on the same TMA tiles (FG_NO_TCGEN05=1 forces that)
             args = (_ptr(q), q.stride(0), _ptr(out), out.stride(0), memory.tensor_maps[2].ptr,
@@ -1021,7 +1213,7 @@ class Ops:
                 _ptr(q), q.stride(0), _ptr(out), out.stride(0), *common,
                 _ptr(tiles.req), _ptr(tiles.tok0), _ptr(tiles.ntok), tiles.n,
                 n_heads, n_kv_heads, head_dim, int(window or 0), keep_first, float(scale), float(softcap or 0.0),
-                _ptr(self.status), _stream()))
+                _ptr(sinks), _ptr(self.status), _stream()))
         singles = ctx.single_tokens()
         fused = out_freqs is not None and tiles.n == 0 and singles.n > 0
         turn = _ptr(out_freqs) if fused else None
@@ -1045,11 +1237,11 @@ class Ops:
                     _ptr(q), q.stride(0), _ptr(out), out.stride(0), memory.tensor_maps[0].ptr,
                     memory.tensor_maps[1].ptr, memory.layer_index, _ptr(block_table),
                     block_table.shape[1], page_size, k_pages.shape[0], _ptr(ctx.pos), *head, pairs, turn,
-                    _ptr(self.status), _stream()))
+                    _ptr(sinks), _ptr(self.status), _stream()))
             else:
                 _check(lib, lib.fg_attention_decode_bf16(
                     _ptr(q), q.stride(0), _ptr(out), out.stride(0), *common, *head, turn, float(softcap or 0.0),
-                    _ptr(self.status), _stream()))
+                    _ptr(sinks), _ptr(self.status), _stream()))
             Ops.launches += 1  # the combine kernel
         return fused
 

@@ -56,6 +56,12 @@ rmsnorm_sum_kernel(float* h, SumTerms terms, const float* __restrict__ row, cons
     }
   }
   if (out == nullptr) return;
+  if (w == nullptr) {
+    // no norm: the summed row itself, in the output's type (the input of a product that reads the stream)
+    __syncthreads();
+    for (int d = threadIdx.x; d < dim; d += SUM_THREADS) out[obase + d] = from_f32<TO>(kept[d]);
+    return;
+  }
   ss = block_sum(ss, scratch);
   const float rstd = rsqrtf(ss / (float)dim + eps);
   const float plus = one_plus ? 1.f : 0.f;
@@ -64,7 +70,8 @@ rmsnorm_sum_kernel(float* h, SumTerms terms, const float* __restrict__ row, cons
 }
 
 // h: float32 [T, dim].  deltas: n_terms pointers to [T, dim] tensors of delta_dtype, with their
-// multiples.  row: float32 [dim] or null.  out: [n_rows, dim] of out_dtype, or null (the sum only).
+// multiples.  row: float32 [dim] or null.  out: [n_rows, dim] of out_dtype, or null (the sum only); with
+// out and no weight the summed rows are stored in out as they are (no norm).
 // rows: null, or n_rows indices into h and the summands to gather (h is then left as it was).
 extern "C" int fg_rmsnorm_sum(float* h, const void* const* deltas, const float* coefs, int n_terms, int delta_dtype,
                               const float* row, const void* w, int w_dtype, int one_plus, void* out, int out_dtype,
@@ -73,7 +80,6 @@ extern "C" int fg_rmsnorm_sum(float* h, const void* const* deltas, const float* 
   FG_CHECK_ARG(dim > 0 && dim <= 48 * 1024 / 4, "fg_rmsnorm_sum: bad dim %d", dim);
   FG_CHECK_ARG(n_terms >= 0 && n_terms <= SUM_MAX_TERMS, "fg_rmsnorm_sum: %d summands (at most %d)", n_terms,
                SUM_MAX_TERMS);
-  FG_CHECK_ARG(out == nullptr || w != nullptr, "fg_rmsnorm_sum: a norm needs its weight");
   SumTerms terms;
   terms.n = n_terms;
   bool vec = dim % 4 == 0 && ((uintptr_t)h & 15) == 0 && (row == nullptr || ((uintptr_t)row & 15) == 0);

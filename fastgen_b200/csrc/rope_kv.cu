@@ -54,7 +54,7 @@ rope_kv_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_s
                const float* __restrict__ v_freqs, T* __restrict__ k_pages, T* __restrict__ v_pages, const int* __restrict__ block_table, int table_width,
                int page_size, int n_pages, int n_heads, int n_kv_heads, int head_dim, int* status,
                bool vec, int heads_per_block, const float* rstd, const float* __restrict__ qn_w,
-               const float* __restrict__ kn_w) {
+               const float* __restrict__ kn_w, int rstd_heads) {
   const int t = blockIdx.x;
   const int r = req[t];
   if (r < 0) return;
@@ -67,8 +67,9 @@ rope_kv_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_s
   const int total = n_heads + 2 * n_kv;  // heads in the order q..., k..., v...
   const int h_end = min(total, (int)(blockIdx.y + 1) * heads_per_block);
   float s = 0.f, c = 1.f, sv = 0.f, cv = 1.f;
-  // queries and keys normed over their whole projection: the token's two factors
-  const float rq = rstd ? rstd[2 * t] : 1.f, rk = rstd ? rstd[2 * t + 1] : 1.f;
+  // queries and keys normed over their whole projection: the token's two factors; with rstd_heads
+  // (= query heads + key heads) every head of the token has a factor of its own
+  const float rq = rstd && !rstd_heads ? rstd[2 * t] : 1.f, rk = rstd && !rstd_heads ? rstd[2 * t + 1] : 1.f;
   if (freqs != nullptr) sincosf((float)p * freqs[j], &s, &c);
   if (v_freqs != nullptr) sincosf((float)p * v_freqs[j], &sv, &cv);
   size_t slot = 0;
@@ -78,8 +79,9 @@ rope_kv_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_s
       T* x = q + (size_t)t * q_stride + h * head_dim + 2 * j;
       float2 val = load_pair<T>(x, vec);
       if (rstd != nullptr) {
-        val.x *= rq * qn_w[h * head_dim + 2 * j];
-        val.y *= rq * qn_w[h * head_dim + 2 * j + 1];
+        const float f = rstd_heads ? rstd[(size_t)t * rstd_heads + h] : rq;
+        val.x *= f * (qn_w ? qn_w[h * head_dim + 2 * j] : 1.f);
+        val.y *= f * (qn_w ? qn_w[h * head_dim + 2 * j + 1] : 1.f);
       }
       store_pair<T>(x, make_float2(val.x * c - val.y * s, val.y * c + val.x * s), vec);
       continue;
@@ -106,8 +108,9 @@ rope_kv_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_s
       const T* x = k + (size_t)t * k_stride + g * head_dim + 2 * j;
       float2 val = load_pair<T>(x, vec);
       if (rstd != nullptr) {
-        val.x *= rk * kn_w[g * head_dim + 2 * j];
-        val.y *= rk * kn_w[g * head_dim + 2 * j + 1];
+        const float f = rstd_heads ? rstd[(size_t)t * rstd_heads + n_heads + g] : rk;
+        val.x *= f * (kn_w ? kn_w[g * head_dim + 2 * j] : 1.f);
+        val.y *= f * (kn_w ? kn_w[g * head_dim + 2 * j + 1] : 1.f);
       }
       store_pair<T>(k_pages + dst, make_float2(val.x * c - val.y * s, val.y * c + val.x * s), vec);
     }
@@ -126,7 +129,8 @@ rope_kv_bf16x8_kernel(__nv_bfloat16* __restrict__ q, int q_stride, const __nv_bf
                       const float* __restrict__ v_freqs, __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages,
                       const int* __restrict__ block_table, int table_width, int page_size, int n_pages,
                       int n_heads, int n_kv_heads, int head_dim, int* status, int heads_per_block,
-                      const float* rstd, const float* __restrict__ qn_w, const float* __restrict__ kn_w) {
+                      const float* rstd, const float* __restrict__ qn_w, const float* __restrict__ kn_w,
+                      int rstd_heads) {
   const int t = blockIdx.x;
   const int r = req[t];
   if (r < 0) return;
@@ -156,16 +160,17 @@ rope_kv_bf16x8_kernel(__nv_bfloat16* __restrict__ q, int q_stride, const __nv_bf
     }
     slot = (size_t)page * n_kv_heads * page_size + (p - logical * page_size);
   }
-  const float rq = rstd ? rstd[2 * t] : 1.f, rk = rstd ? rstd[2 * t + 1] : 1.f;
-  // nw: the eight norm weights of this piece of the head (null: no norm), r: the token's factor
+  const float rq = rstd && !rstd_heads ? rstd[2 * t] : 1.f, rk = rstd && !rstd_heads ? rstd[2 * t + 1] : 1.f;
+  // nw: the eight norm weights of this piece of the head (null: ones), r: the factor of the token
+  // (or of this head of the token)
   auto rotate = [&](uint4 raw, const float* nw, float r) {
     __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&raw);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       float2 val = __bfloat1622float2(h2[i]);
-      if (nw != nullptr) {
-        val.x *= r * nw[2 * i];
-        val.y *= r * nw[2 * i + 1];
+      if (rstd != nullptr) {
+        val.x *= r * (nw ? nw[2 * i] : 1.f);
+        val.y *= r * (nw ? nw[2 * i + 1] : 1.f);
       }
       h2[i] = __floats2bfloat162_rn(val.x * cs[i] - val.y * sn[i], val.y * cs[i] + val.x * sn[i]);
     }
@@ -199,7 +204,8 @@ rope_kv_bf16x8_kernel(__nv_bfloat16* __restrict__ q, int q_stride, const __nv_bf
       if (h >= h_end) continue;
       if (h < n_heads) {
         *reinterpret_cast<uint4*>(q + (size_t)t * q_stride + h * head_dim + piece * 8) =
-            rotate(raw[u], rstd ? qn_w + h * head_dim + piece * 8 : nullptr, rq);
+            rotate(raw[u], qn_w ? qn_w + h * head_dim + piece * 8 : nullptr,
+                   rstd_heads ? rstd[(size_t)t * rstd_heads + h] : rq);
         continue;
       }
       const bool is_v = h >= n_heads + n_kv;
@@ -207,7 +213,8 @@ rope_kv_bf16x8_kernel(__nv_bfloat16* __restrict__ q, int q_stride, const __nv_bf
       const size_t dst = (slot + (size_t)g * page_size) * head_dim + piece * 8;
       *reinterpret_cast<uint4*>((is_v ? v_pages : k_pages) + dst) =
           is_v ? (v_freqs != nullptr ? rotate_v(raw[u]) : raw[u])
-               : rotate(raw[u], rstd ? kn_w + g * head_dim + piece * 8 : nullptr, rk);
+               : rotate(raw[u], kn_w ? kn_w + g * head_dim + piece * 8 : nullptr,
+                        rstd_heads ? rstd[(size_t)t * rstd_heads + n_heads + g] : rk);
     }
   }
 }
@@ -255,6 +262,58 @@ extern "C" int fg_qk_rstd(const void* q, long q_stride, int nq, int count_q, con
   return 0;
 }
 
+// Per-head factors of queries and keys: out[t, h] for the token's query heads, then its key heads.
+// With `norm` a head's factor is rsqrt(mean of its first `real_dim` columns squared + eps) (an RMS norm
+// per head; the head's padding columns hold zeros); with temp_every > 0 a query head's factor is also
+// multiplied by 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1) at position p: a query temperature
+// that grows in steps with the position.  A warp a (token, head).
+template <typename T>
+__global__ void __launch_bounds__(128)
+qk_head_factors_kernel(const T* q, long q_stride, const T* k, long k_stride, int n_heads, int n_kv_heads,
+                       int head_dim, int real_dim, int norm, float eps, float temp_coef, int temp_every,
+                       const int* __restrict__ pos, const int* __restrict__ req, float* __restrict__ out, int n_tokens) {
+  const int heads = n_heads + n_kv_heads;
+  const long item = (long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (item >= (long)n_tokens * heads) return;
+  const int t = (int)(item / heads), h = (int)(item % heads), lane = threadIdx.x & 31;
+  if (req[t] < 0) return;
+  float f = 1.f;
+  if (norm) {
+    const T* x = h < n_heads ? q + (size_t)t * q_stride + (size_t)h * head_dim
+                             : k + (size_t)t * k_stride + (size_t)(h - n_heads) * head_dim;
+    float ss = 0.f;
+    for (int d = lane; d < real_dim; d += 32) {
+      const float v = to_f32<T>(x[d]);
+      ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
+    f = rsqrtf(ss / (float)real_dim + eps);
+  }
+  if (temp_every > 0 && h < n_heads) f *= 1.f + temp_coef * logf((float)((pos[t] + 1) / temp_every) + 1.f);
+  if (lane == 0) out[(size_t)t * heads + h] = f;
+}
+
+extern "C" int fg_qk_head_factors(const void* q, long q_stride, const void* k, long k_stride, int dtype, int n_heads,
+                                  int n_kv_heads, int head_dim, int real_dim, int norm, float eps, float temp_coef,
+                                  int temp_every, const int* pos, const int* req, float* out, int n_tokens,
+                                  cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  FG_CHECK_ARG(n_heads > 0 && n_kv_heads >= 0 && real_dim > 0 && real_dim <= head_dim && (n_kv_heads == 0 || k || !norm),
+               "fg_qk_head_factors: bad sizes");
+  const long items = (long)n_tokens * (n_heads + n_kv_heads);
+  const unsigned grid = (unsigned)((items + 3) / 4);
+  if (dtype == FG_F32)
+    qk_head_factors_kernel<float><<<grid, 128, 0, stream>>>((const float*)q, q_stride, (const float*)k, k_stride,
+                                                            n_heads, n_kv_heads, head_dim, real_dim, norm, eps,
+                                                            temp_coef, temp_every, pos, req, out, n_tokens);
+  else
+    qk_head_factors_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(
+        (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k, k_stride, n_heads, n_kv_heads, head_dim, real_dim,
+        norm, eps, temp_coef, temp_every, pos, req, out, n_tokens);
+  FG_CHECK_LAUNCH("fg_qk_head_factors");
+  return 0;
+}
+
 // q: [T, n_heads*head_dim] with row stride q_stride (elements), rotated in place.
 // k, v: [T, n_kv_heads*head_dim] with their strides, or both null (queries only).
 // freqs: float32 [head_dim/2] or null for no rotation of queries and keys; v_freqs: the same
@@ -264,10 +323,15 @@ extern "C" int fg_rope_kv_write(void* q, int q_stride, const void* k, int k_stri
                                 const float* freqs, const float* v_freqs, void* k_pages, void* v_pages,
                                 const int* block_table, int table_width, int page_size, int n_pages,
                                 int n_tokens, int n_heads, int n_kv_heads, int head_dim, int* status,
-                                const float* rstd, const float* qn_w, const float* kn_w, cudaStream_t stream) {
+                                const float* rstd, const float* qn_w, const float* kn_w, int rstd_heads,
+                                cudaStream_t stream) {
+  // rstd: null, or float32 factors by which queries and keys are multiplied before they turn: [T, 2]
+  // (a token's queries, its keys) when rstd_heads is 0, else [T, rstd_heads] with rstd_heads = n_heads +
+  // n_kv_heads (every query head, then every key head).  qn_w / kn_w: per-column weights that join the
+  // factors, or null for ones.
   if (n_tokens == 0) return 0;
-  FG_CHECK_ARG(rstd == nullptr || (qn_w != nullptr && (k == nullptr || kn_w != nullptr)),
-               "fg_rope_kv_write: a norm of queries and keys needs its weights");
+  FG_CHECK_ARG(rstd_heads == 0 || (rstd != nullptr && rstd_heads == n_heads + n_kv_heads),
+               "fg_rope_kv_write: %d factors a token for %d + %d heads", rstd_heads, n_heads, n_kv_heads);
   FG_CHECK_ARG(head_dim > 0 && head_dim % 2 == 0, "fg_rope_kv_write: head_dim %d must be even", head_dim);
   FG_CHECK_ARG((k == nullptr) == (v == nullptr), "fg_rope_kv_write: k and v must both be given or both null");
   FG_CHECK_ARG(k == nullptr || (k_pages && v_pages && block_table && page_size > 0),
@@ -290,7 +354,7 @@ extern "C" int fg_rope_kv_write(void* q, int q_stride, const void* k, int k_stri
     rope_kv_bf16x8_kernel<<<grid, threads, 0, stream>>>(
         (__nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v, v_stride, pos, req,
         freqs, v_freqs, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, block_table, table_width, page_size,
-        n_pages, n_heads, n_kv_heads, head_dim, status, ipt, rstd, qn_w, kn_w);
+        n_pages, n_heads, n_kv_heads, head_dim, status, ipt, rstd, qn_w, kn_w, rstd_heads);
     FG_CHECK_LAUNCH("fg_rope_kv_write");
     return 0;
   }
@@ -298,12 +362,12 @@ extern "C" int fg_rope_kv_write(void* q, int q_stride, const void* k, int k_stri
     rope_kv_kernel<float><<<grid, threads, 0, stream>>>(
         (float*)q, q_stride, (const float*)k, k_stride, (const float*)v, v_stride, pos, req, freqs, v_freqs,
         (float*)k_pages, (float*)v_pages, block_table, table_width, page_size, n_pages, n_heads,
-        n_kv_heads, head_dim, status, vec, ipt, rstd, qn_w, kn_w);
+        n_kv_heads, head_dim, status, vec, ipt, rstd, qn_w, kn_w, rstd_heads);
   else if (dtype == FG_BF16)
     rope_kv_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
         (__nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v,
         v_stride, pos, req, freqs, v_freqs, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, block_table,
-        table_width, page_size, n_pages, n_heads, n_kv_heads, head_dim, status, vec, ipt, rstd, qn_w, kn_w);
+        table_width, page_size, n_pages, n_heads, n_kv_heads, head_dim, status, vec, ipt, rstd, qn_w, kn_w, rstd_heads);
   else
     FG_CHECK_ARG(false, "fg_rope_kv_write: bad dtype %d", dtype);
   FG_CHECK_LAUNCH("fg_rope_kv_write");

@@ -76,6 +76,8 @@ def _collect_specs(args: ModelArgs, blocks: Sequence[Block], final_norm, embedde
     ordered.extend(final_norm.weight_specs())
     if args.step_table_name is not None:
         ordered.append(WeightSpec(args.step_table_name, (args.step_table_rows, args.dim), ("normal", 0.1)))
+    if args.pass_input_name is not None:
+        ordered.append(WeightSpec(args.pass_input_name, (args.dim, 2 * args.dim), ("normal", (2 * args.dim) ** -0.5)))
     if not args.tie_embeddings:
         ordered.append(WeightSpec(args.output_name, (args.vocab_size, args.dim)))
     for s in ordered:
@@ -102,6 +104,9 @@ class Model:
         self.embedding: Optional[torch.Tensor] = None
         self.output: Optional[torch.Tensor] = None
         self.step_table: Optional[torch.Tensor] = None  # float32 [rows, dim]
+        # the two halves of the map that opens a pass: what meets the stream, what meets the embedder's output
+        self.pass_stream: Optional[torch.Tensor] = None
+        self.pass_embed: Optional[torch.Tensor] = None
 
     # -- description -----------------------------------------------------------
     def weight_specs(self) -> List[WeightSpec]:
@@ -144,6 +149,8 @@ class Model:
                     add_part(v)
         add(self.output)
         add(self.step_table)
+        add(self.pass_stream)
+        add(self.pass_embed)
         for block in self.blocks:
             for part in block.parts():
                 add_part(part)
@@ -168,6 +175,10 @@ class Model:
         if self.args.step_table_name is not None:
             # the vectors join the float32 residual sum: float32 whatever they were stored in
             self.step_table = tensors[self.args.step_table_name].float().contiguous()
+        if self.args.pass_input_name is not None:
+            w = tensors[self.args.pass_input_name].to(dt)
+            self.pass_stream = w[:, : self.args.dim].contiguous()
+            self.pass_embed = w[:, self.args.dim :].contiguous()
 
     @staticmethod
     def load(model_dir, dtype: torch.dtype, device) -> "Model":
@@ -211,6 +222,22 @@ class Model:
         return model
 
     # -- forward -----------------------------------------------------------------
+    def _mix_input(self, h, pending, embed_part):
+        """``x <- W [x; x0]``: what is pending joins the stream (float32), the stream meets its half of
+        the map, and the embedder's half (``embed_part``, float32) is left pending: the next norm's
+        kernel adds it."""
+        ops = self.ops
+        delta, delta_norm = split_pending(pending)
+        if delta is not None and delta_norm is not None:
+            delta = delta_norm.forward(delta, out_dtype=torch.float32)
+        total = ScaledSum.of(delta)
+        if len(total.terms) > 4 or len({term.dtype for term, _ in total.terms}) > 1:
+            total.add_into(h, ops)
+            total = ScaledSum([])
+        x = torch.empty(h.shape, dtype=ops.act_dtype, device=h.device)
+        ops.rmsnorm_sum(h, total.terms, None, 0.0, out=x, row=total.row)
+        return ops.linear(x, self.pass_stream, out_dtype=torch.float32), ScaledSum([(embed_part, 1.0)])
+
     def forward(self, ctx, memories) -> Optional[torch.Tensor]:
         """Run the step's tokens through the schedule.  Returns float32 logits
         ``[len(ctx.want_rows), vocab]`` (``None`` when no logits are wanted).
@@ -223,7 +250,16 @@ class Model:
         h = torch.empty(shape, dtype=torch.float32, device=ops.device)
         self.embedder.forward(ctx, getattr(memories, "embedder_state", None), h)
         pending = None
+        embed_part = None
+        if self.pass_embed is not None:
+            # the embedder's output meets its half of the map once a step: that product is the same
+            # before every pass
+            x0 = torch.empty((t, self.args.dim), dtype=ops.act_dtype, device=ops.device)
+            ops.rmsnorm_sum(h, (), None, 0.0, out=x0)
+            embed_part = ops.linear(x0, self.pass_embed, out_dtype=torch.float32)
         for e, entry in enumerate(self.args.schedule):
+            if entry.mix_input:
+                h, pending = self._mix_input(h, pending, embed_part)
             if entry.step_row is not None:
                 # the pass's step vector joins whatever the layer before left pending
                 pending = ScaledSum.of(pending).plus(ScaledSum([], row=self.step_table[entry.step_row]))

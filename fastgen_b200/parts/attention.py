@@ -6,7 +6,7 @@ from typing import List, Optional
 
 import torch
 
-from .base import CacheSpec, Mixer, WeightSpec, make_position, register_mixer
+from .base import CacheSpec, Mixer, StateSpec, WeightSpec, make_position, register_mixer
 from .params import AttentionParams, SigmoidAttentionParams
 
 
@@ -59,7 +59,11 @@ class GQAAttention(Mixer):
     ``AttentionParams.kernel_head_dim``); rotary encodings that turn a part of the head, in
     either pairing (half-split rows are reordered at bind time, which changes no score);
     values turned by their position on their way into the cache and outputs turned back by
-    the query's position.
+    the query's position.  Further options: an RMS norm of queries and keys per head; values that are
+    the keys as projected (no value projection); a query temperature that grows with the position; a
+    sink per head in the softmax's denominator; a sigmoid gate per head on the output; a short causal
+    convolution over time on q, k and v directly after the projection, whose last inputs are the
+    request's fixed-size state beside its pages.
     """
 
     params: AttentionParams
@@ -75,6 +79,13 @@ class GQAAttention(Mixer):
         self.hd = p.kernel_head_dim
         self.q_width = p.n_heads * self.hd
         self.kv_width = p.n_kv_heads * self.hd
+        self.o_bias = p.bias if p.o_bias is None else p.o_bias
+        #: channels that pass the convolution: q, k and v as the kernels hold them (padded heads)
+        self.conv_channels = self.q_width + 2 * self.kv_width
+        #: the fused few-token kernel (projection, rotation, page write) knows none of these
+        self.plain = not (p.qk_norm or p.q_temp or p.conv or p.head_gate)
+        if p.q_temp and p.qk_norm == "projection":
+            raise ValueError("a query temperature joins the per-head factors: not with a norm over the projection")
 
     def weight_specs(self) -> List[WeightSpec]:
         p = self.params
@@ -83,26 +94,51 @@ class GQAAttention(Mixer):
         specs = [
             WeightSpec(self.names["wq"], (q, p.dim)),
             WeightSpec(self.names["wk"], (k, p.dim)),
-            WeightSpec(self.names["wv"], (v, p.dim)),
-            WeightSpec(self.names["wo"], (p.dim, o)),
         ]
+        if not p.shared_kv:
+            specs.append(WeightSpec(self.names["wv"], (v, p.dim)))
+        specs.append(WeightSpec(self.names["wo"], (p.dim, o)))
         if p.bias:
             specs += [
                 WeightSpec(self.names["bq"], (q,)),
                 WeightSpec(self.names["bk"], (k,)),
-                WeightSpec(self.names["bv"], (v,)),
-                WeightSpec(self.names["bo"], (p.dim,)),
             ]
-        if p.qk_norm:
+            if not p.shared_kv:
+                specs.append(WeightSpec(self.names["bv"], (v,)))
+            if self.o_bias:
+                specs.append(WeightSpec(self.names["bo"], (p.dim,)))
+        if p.qk_norm == "projection":
             specs += [
                 WeightSpec(self.names["q_norm"], (q,), ("ones",)),
                 WeightSpec(self.names["k_norm"], (k,), ("ones",)),
+            ]
+        elif p.qk_norm == "head":
+            specs += [
+                WeightSpec(self.names["q_norm"], (p.head_dim,), ("ones",)),
+                WeightSpec(self.names["k_norm"], (p.head_dim,), ("ones",)),
+            ]
+        if p.sink:
+            specs.append(WeightSpec(self.names["sink"], (p.n_heads,), ("normal", 1.0)))
+        if p.head_gate:
+            specs.append(WeightSpec(self.names["wg"], (p.n_heads, p.dim)))
+        if p.conv:
+            specs += [
+                WeightSpec(self.names["conv_q"], (q, p.conv), ("normal", 0.3)),
+                WeightSpec(self.names["conv_k"], (k, p.conv), ("normal", 0.3)),
+                WeightSpec(self.names["conv_v"], (v, p.conv), ("normal", 0.3)),
             ]
         return specs
 
     def cache_spec(self) -> Optional[CacheSpec]:
         p = self.params
         return CacheSpec(p.n_kv_heads, self.hd, p.window, keep_first=p.keep_first if p.window else 0)
+
+    def state_spec(self) -> Optional[StateSpec]:
+        p = self.params
+        if not p.conv:
+            return None
+        # the convolution's last inputs: conv - 1 rows of the projected q, k and v
+        return StateSpec((max(1, p.conv - 1) * self.conv_channels,))
 
     def _rot_dims(self, position, size: int) -> int:
         params = getattr(position, "params", None)
@@ -122,10 +158,23 @@ class GQAAttention(Mixer):
         vd = self.v_head_dim
         rotates = not isinstance(self.position.table(ops.device), type(None))
         qk_pos = self.position if rotates else None
+        if p.shared_kv:
+            # the values are the keys as projected: the key rows once more, in the values' place
+            tensors = dict(tensors, wv=tensors["wk"])
+            if p.bias:
+                tensors["bv"] = tensors["bk"]
         wq = self._rows(tensors["wq"], p.n_heads, p.head_dim, p.qk_layout, qk_pos)
         wk = self._rows(tensors["wk"], p.n_kv_heads, p.head_dim, p.qk_layout, qk_pos)
         wv = self._rows(tensors["wv"], p.n_kv_heads, vd, p.v_layout, self.value_position)
-        self.wqkv = torch.cat([wq, wk, wv], dim=0).to(dt).contiguous()
+        parts = [wq, wk, wv]
+        self.gate_rows = 0
+        if p.head_gate:
+            # the gate's rows ride in the same product (padded to whole groups of 8 rows)
+            self.gate_rows = -(-p.n_heads // 8) * 8
+            wg = tensors["wg"].new_zeros((self.gate_rows, p.dim))
+            wg[: p.n_heads] = tensors["wg"]
+            parts.append(wg)
+        self.wqkv = torch.cat(parts, dim=0).to(dt).contiguous()
         # the output projection's columns follow the value heads' rows
         wo_t = self._rows(tensors["wo"].t(), p.n_heads, vd, p.v_layout, self.value_position)
         self.wo = wo_t.t().to(dt).contiguous()
@@ -134,14 +183,25 @@ class GQAAttention(Mixer):
             bq = self._rows(tensors["bq"], p.n_heads, p.head_dim, p.qk_layout, qk_pos)
             bk = self._rows(tensors["bk"], p.n_kv_heads, p.head_dim, p.qk_layout, qk_pos)
             bv = self._rows(tensors["bv"], p.n_kv_heads, vd, p.v_layout, self.value_position)
-            self.bqkv = torch.cat([bq, bk, bv], dim=0).to(dt).contiguous()
-            self.bo = tensors["bo"].to(dt).contiguous()
+            self.bqkv = torch.cat([bq, bk, bv, bq.new_zeros(self.gate_rows)], dim=0).to(dt).contiguous()
+            self.bo = tensors["bo"].to(dt).contiguous() if self.o_bias else None
         self.q_norm = self.k_norm = None
         if p.qk_norm:
             # the norm's weights follow their projection's rows (a head's padding has weight zero);
-            # they enter float32 arithmetic
-            self.q_norm = self._rows(tensors["q_norm"], p.n_heads, p.head_dim, p.qk_layout, qk_pos).float().contiguous()
-            self.k_norm = self._rows(tensors["k_norm"], p.n_kv_heads, p.head_dim, p.qk_layout, qk_pos).float().contiguous()
+            # they enter float32 arithmetic.  Weights of one head's size are shared by the heads.
+            qn, kn = tensors["q_norm"], tensors["k_norm"]
+            if p.qk_norm == "head":
+                qn, kn = qn.repeat(p.n_heads), kn.repeat(p.n_kv_heads)
+            self.q_norm = self._rows(qn, p.n_heads, p.head_dim, p.qk_layout, qk_pos).float().contiguous()
+            self.k_norm = self._rows(kn, p.n_kv_heads, p.head_dim, p.qk_layout, qk_pos).float().contiguous()
+        self.sinks = tensors["sink"].float().contiguous() if p.sink else None
+        self.conv_w = None
+        if p.conv:
+            self.conv_w = torch.cat([
+                self._rows(tensors["conv_q"], p.n_heads, p.head_dim, p.qk_layout, qk_pos),
+                self._rows(tensors["conv_k"], p.n_kv_heads, p.head_dim, p.qk_layout, qk_pos),
+                self._rows(tensors["conv_v"], p.n_kv_heads, vd, p.v_layout, self.value_position),
+            ], dim=0).float().contiguous()
         self.freqs = self._table(self.position)
         self.v_freqs = self.v_unfreqs = None
         if self.value_position is not None:
@@ -162,29 +222,46 @@ class GQAAttention(Mixer):
         back already (values cached turned by their positions): the kernels do it where they can."""
         p = self.params
         return self.ops.attention(q, o, memory, ctx, p.n_heads, p.n_kv_heads, self.hd, p.window, self.scale,
-                                  out_freqs=self.v_unfreqs, keep_first=p.keep_first, softcap=p.softcap)
+                                  out_freqs=self.v_unfreqs, keep_first=p.keep_first, softcap=p.softcap,
+                                  sinks=self.sinks)
 
     def forward(self, x, ctx, memory):
         p, ops = self.params, self.ops
         t = x.shape[0]
         q = None
-        if memory.writes and x.dtype == torch.bfloat16 and not p.qk_norm:
+        gate = None
+        if memory.writes and x.dtype == torch.bfloat16 and self.plain:
             # a few tokens: projection, rotation and page write in one kernel
             q = ops.qkv_rope_write(x, self.wqkv, ctx.pos, ctx.req, self.freqs, memory,
                                    p.n_heads, p.n_kv_heads, self.hd, bias=self.bqkv, v_freqs=self.v_freqs)
         if q is None:
             if memory.writes:
                 qkv = ops.linear(x, self.wqkv, bias=self.bqkv)
+                if p.head_gate:
+                    gate = qkv[:, self.conv_channels : self.conv_channels + p.n_heads]
+                if p.conv:
+                    # the convolution reads the projected rows (and the state's last ones) and gives
+                    # q, k and v in the compute type
+                    qkv = ops.time_conv(qkv, 0, self.conv_channels, self.conv_w, None, memory.state, 0, p.conv, ctx,
+                                        out_dtype=x.dtype)
                 q = qkv[:, : self.q_width]
                 k = qkv[:, self.q_width : self.q_width + self.kv_width]
-                v = qkv[:, self.q_width + self.kv_width :]
+                v = qkv[:, self.q_width + self.kv_width : self.q_width + 2 * self.kv_width]
             else:
                 # this run reads another run's cache: only queries are needed
+                if p.conv or p.head_gate or p.qk_norm == "head" or p.q_temp:
+                    raise NotImplementedError("a run that reads another run's cache takes plain queries")
                 bq = self.bqkv[: self.q_width] if self.bqkv is not None else None
                 q = ops.linear(x, self.wqkv[: self.q_width], bias=bq)
                 k = v = None
             qk_norm = None
-            if p.qk_norm:
+            if p.qk_norm == "head" or p.q_temp:
+                # a factor per (token, head): the head's RMS norm and, for queries, the temperature of
+                # the token's position; the kernel that rotates multiplies by them and by the weights
+                factors = ops.qk_head_factors(q, k, ctx.pos, ctx.req, p.n_heads, p.n_kv_heads, self.hd, p.head_dim,
+                                              norm_eps=p.qk_norm_eps if p.qk_norm else None, temp=p.q_temp)
+                qk_norm = (factors, self.q_norm, self.k_norm)
+            elif p.qk_norm:
                 # a norm over the whole projection: the token's two factors first, then the kernel
                 # that rotates multiplies by them and by the weights
                 rstd = ops.qk_rstd(q, k, p.n_heads * p.head_dim, p.n_kv_heads * p.head_dim, p.qk_norm_eps, ctx.req)
@@ -199,6 +276,8 @@ class GQAAttention(Mixer):
         if self.v_unfreqs is not None and not turned:
             # the sum over values that were turned by their own positions is turned back by the query's
             ops.rotate_heads(o, ctx.pos, ctx.req, self.v_unfreqs, p.n_heads, self.hd)
+        if gate is not None:
+            ops.head_gate(o, gate, ctx.req, p.n_heads, self.hd)
         return ops.linear(o, self.wo, bias=self.bo)
 
 

@@ -8,7 +8,7 @@ from the model they are in.  The architecture code fills these from the keys of
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Optional
+from typing import Optional, Tuple
 
 
 @dataclass(frozen=True)
@@ -102,15 +102,40 @@ class AttentionParams:
     keep_first: int = 0
     #: ``"projection"``: queries and keys pass an RMS norm over their whole projection (all heads of
     #: a token at once, eps ``qk_norm_eps``, plain weights ``q_norm`` / ``k_norm`` of that size) before
-    #: they are rotated; ``None``: none
+    #: they are rotated; ``"head"``: an RMS norm per head, weights of ``head_dim`` numbers shared by the
+    #: heads; ``None``: none
     qk_norm: Optional[str] = None
     qk_norm_eps: float = 1e-6
     #: a scaled score ``s`` enters the softmax as ``softcap * tanh(s / softcap)`` (``None``: as it is)
     softcap: Optional[float] = None
+    #: whether the output projection has a bias when ``bias`` is set (``None``: as the others)
+    o_bias: Optional[bool] = None
+    #: the values are the keys as projected: the model has no value projection (tensor ``wv``), and
+    #: ``v_head_dim`` equals ``head_dim``
+    shared_kv: bool = False
+    #: ``(coef, every)``: the query at position ``p`` is multiplied by
+    #: ``1 + coef * ln(floor((p + 1) / every) + 1)``, a temperature that grows in steps
+    q_temp: Optional[Tuple[float, int]] = None
+    #: the softmax's denominator also holds ``exp(sink[h])`` for query head ``h`` (tensor ``sink``): a score
+    #: without a key or a value, not scaled, counted once
+    sink: bool = False
+    #: head ``h``'s output is multiplied by ``sigmoid(wg x)[h]`` before the output projection (tensor
+    #: ``wg`` [heads, dim]; ``x`` is the mixer's input)
+    head_gate: bool = False
+    #: taps of a causal convolution over time on every channel of q, k and v, directly after the
+    #: projection (tensors ``conv_q``, ``conv_k``, ``conv_v`` [channels, taps], no bias; 0: none).  The
+    #: last ``conv - 1`` projected rows of a sequence are its state
+    conv: int = 0
 
     def __post_init__(self) -> None:
-        if self.qk_norm not in (None, "projection"):
-            raise ValueError(f"qk_norm must be None or 'projection', got {self.qk_norm!r}")
+        if self.qk_norm not in (None, "projection", "head"):
+            raise ValueError(f"qk_norm must be None, 'projection' or 'head', got {self.qk_norm!r}")
+        if self.shared_kv and (self.v_head_dim or self.head_dim) != self.head_dim:
+            raise ValueError("values that are the keys have the keys' size")
+        if self.q_temp is not None and (len(self.q_temp) != 2 or int(self.q_temp[1]) < 1):
+            raise ValueError(f"a query temperature is (coef, every >= 1), got {self.q_temp!r}")
+        if not 0 <= self.conv <= 8:
+            raise ValueError(f"the convolution takes up to 8 taps, got {self.conv}")
         if self.softcap is not None and self.softcap <= 0:
             raise ValueError(f"a cap on the scores must be positive, got {self.softcap}")
         for name, layout in (("qk_layout", self.qk_layout), ("v_layout", self.v_layout)):
@@ -174,14 +199,14 @@ class RMSNormParams:
 @dataclass(frozen=True)
 class DenseMLPParams:
     """Dense feed-forward ``down(act(up x))`` without a gate; ``act`` is ``"gelu_erf"`` (the
-    exact GELU) or ``"gelu_tanh"``."""
+    exact GELU), ``"gelu_tanh"`` or ``"relu2"`` (the square of ReLU)."""
 
     dim: int
     ffn_dim: int
     act: str = "gelu_erf"
 
     def __post_init__(self) -> None:
-        if self.act not in ("gelu_erf", "gelu_tanh"):
+        if self.act not in ("gelu_erf", "gelu_tanh", "relu2"):
             raise ValueError(f"unknown activation {self.act!r}")
 
 
@@ -347,6 +372,10 @@ class SideBySideParams:
     right: object
     left_scale: float = 1.0
     right_scale: float = 1.0
+    #: ``PartSpec``s of norms that the two outputs pass before they are multiplied and added
+    #: (``None``: none)
+    left_norm: Optional[object] = None
+    right_norm: Optional[object] = None
 
 
 @dataclass(frozen=True)
@@ -362,12 +391,35 @@ class RoutedExpertsParams:
     top: int
     correction: bool = True
     renormalize: bool = False
+    #: the experts' scores: ``"softmax"`` over all experts or ``"sigmoid"`` of each logit
+    score: str = "softmax"
+    #: ``(count, keep)``: the experts form ``count`` equal groups of neighbours; a group's score is the
+    #: sum of its ``group_top`` largest scores and only experts of the ``keep`` best groups can be chosen
+    groups: Optional[Tuple[int, int]] = None
+    group_top: int = 2
+    #: added to the chosen scores' sum before ``renormalize`` divides by it
+    renorm_eps: float = 0.0
+    #: the weights are multiplied by it at the end
+    weight_scale: float = 1.0
+    #: ``"silu_gate"``: experts ``down(silu(gate x) * up x)``; an activation of the dense feed-forward
+    #: (``"relu2"``, ...): experts ``down(act(up x))`` without a gate (no tensors ``w1``; ``w3`` is up)
+    act: str = "silu_gate"
+    #: a ``PartSpec`` of a feed-forward that every token also passes and whose output is added
+    shared: Optional[object] = None
 
     def __post_init__(self) -> None:
         if not 1 <= self.top <= self.n_experts:
             raise ValueError(f"a token cannot use {self.top} of {self.n_experts} experts")
         if self.n_experts > 256:
             raise ValueError(f"the router takes up to 256 experts, got {self.n_experts}")
+        if self.score not in ("softmax", "sigmoid"):
+            raise ValueError(f"unknown kind of score {self.score!r}")
+        if self.groups is not None:
+            count, keep = self.groups
+            if count < 1 or self.n_experts % count or not 1 <= keep <= count:
+                raise ValueError(f"{self.n_experts} experts cannot form {count} equal groups of which {keep} are kept")
+            if keep * (self.n_experts // count) < self.top:
+                raise ValueError(f"{keep} groups of {self.n_experts // count} experts cannot hold {self.top} choices")
 
 
 @dataclass(frozen=True)
@@ -376,3 +428,45 @@ class ParallelBlockParams:
     with ``h = norm(x)``."""
 
     residual_mult: float = 1.0
+
+
+@dataclass(frozen=True)
+class MatrixMemoryParams:
+    """The matrix memory with exponential gates (the mLSTM of xLSTM): ``n_heads`` heads with a state
+    of ``head_dim`` x ``v_head_dim`` each, a normaliser vector and a running maximum that starts at
+    zero.  The log gates are ``cap * tanh(x / cap)`` of their sums plus biases (the forget gate then
+    passes ``logsigmoid``); the read-out is divided by ``max(|n . q|, exp(-m)) + 1e-6``, by its root mean
+    square per head (``eps``), multiplied by a weight over all heads and by a sigmoid gate."""
+
+    dim: int
+    n_heads: int
+    head_dim: int
+    v_head_dim: int
+    gate_cap: float
+    eps: float
+
+    def __post_init__(self) -> None:
+        if not 1 <= self.head_dim <= 256:
+            raise ValueError(f"the state takes 1 to 256 rows a head, got {self.head_dim}")
+        if self.gate_cap <= 0:
+            raise ValueError(f"the cap of the gates must be positive, got {self.gate_cap}")
+
+
+@dataclass(frozen=True)
+class GatedLinearRecurrenceParams:
+    """Griffin's recurrent block: two branches of ``width`` channels, ``gelu_tanh(W_y x + b)`` and a
+    causal convolution (``conv`` taps, with bias) of ``W_x x + b`` that feeds the real-gated linear
+    recurrent unit ``S <- a S + sqrt(1 - a^2) i u`` with ``a = exp(-decay r softplus(lam))``; the gates
+    ``r`` and ``i`` are sigmoids of block-diagonal maps (``blocks`` equal blocks) of ``u``."""
+
+    dim: int
+    width: int
+    blocks: int
+    conv: int
+    decay: float = 8.0
+
+    def __post_init__(self) -> None:
+        if self.width % self.blocks:
+            raise ValueError(f"{self.width} channels cannot form {self.blocks} equal blocks")
+        if not 1 <= self.conv <= 8:
+            raise ValueError(f"the convolution takes 1 to 8 taps, got {self.conv}")

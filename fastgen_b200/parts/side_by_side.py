@@ -4,7 +4,9 @@ from __future__ import annotations
 
 from typing import List, Optional
 
-from .base import CacheSpec, Mixer, ScaledSum, StateSpec, WeightSpec, make_mixer, register_mixer
+import torch
+
+from .base import CacheSpec, Mixer, ScaledSum, StateSpec, WeightSpec, make_mixer, make_norm, register_mixer
 from .params import SideBySideParams
 
 
@@ -15,7 +17,8 @@ class SideBySide(Mixer):
     and at most one may keep a fixed-size state: both are handed the layer's memory and each takes
     from it what it asked for.  The result is returned as a sum that has not been formed (a
     :class:`~fastgen_b200.parts.base.ScaledSum`): the kernel that adds it to the residual stream
-    multiplies the two outputs by their scales in float32.
+    multiplies the two outputs by their scales in float32.  With ``left_norm`` / ``right_norm`` an
+    output passes a norm of its own first (its result stays float32 on its way into the sum).
     """
 
     params: SideBySideParams
@@ -25,13 +28,19 @@ class SideBySide(Mixer):
         p = self.params
         self.left = make_mixer(p.left)
         self.right = make_mixer(p.right)
+        self.left_norm = make_norm(p.left_norm) if p.left_norm is not None else None
+        self.right_norm = make_norm(p.right_norm) if p.right_norm is not None else None
         for what in ("cache_spec", "state_spec"):
             if getattr(self.left, what)() is not None and getattr(self.right, what)() is not None:
                 raise ValueError(f"both mixers of a side-by-side pair ask for a {what.split('_')[0]}: a layer has one")
         self.graph_safe = self.left.graph_safe and self.right.graph_safe
 
     def weight_specs(self) -> List[WeightSpec]:
-        return self.left.weight_specs() + self.right.weight_specs()
+        specs = self.left.weight_specs() + self.right.weight_specs()
+        for norm in (self.left_norm, self.right_norm):
+            if norm is not None:
+                specs += norm.weight_specs()
+        return specs
 
     def cache_spec(self) -> Optional[CacheSpec]:
         return self.left.cache_spec() or self.right.cache_spec()
@@ -43,11 +52,19 @@ class SideBySide(Mixer):
         # the two mixers' tensors arrive under their checkpoint names (see ``names`` below)
         self.left.bind({local: tensors["left." + local] for local in self.left.names}, ops)
         self.right.bind({local: tensors["right." + local] for local in self.right.names}, ops)
+        if self.left_norm is not None:
+            self.left_norm.bind({local: tensors["left_norm." + local] for local in self.left_norm.names}, ops)
+        if self.right_norm is not None:
+            self.right_norm.bind({local: tensors["right_norm." + local] for local in self.right_norm.names}, ops)
 
     @property
     def names(self):
         out = {"left." + k: v for k, v in self.left.names.items()}
         out.update({"right." + k: v for k, v in self.right.names.items()})
+        if self.left_norm is not None:
+            out.update({"left_norm." + k: v for k, v in self.left_norm.names.items()})
+        if self.right_norm is not None:
+            out.update({"right_norm." + k: v for k, v in self.right_norm.names.items()})
         return out
 
     @names.setter
@@ -56,8 +73,13 @@ class SideBySide(Mixer):
 
     def forward(self, x, ctx, memory):
         p = self.params
-        left = ScaledSum.of(self.left.forward(x, ctx, memory), p.left_scale)
-        return left.plus(ScaledSum.of(self.right.forward(x, ctx, memory), p.right_scale))
+        left = self.left.forward(x, ctx, memory)
+        right = self.right.forward(x, ctx, memory)
+        if self.left_norm is not None:
+            left = self.left_norm.forward(left, out_dtype=torch.float32)
+        if self.right_norm is not None:
+            right = self.right_norm.forward(right, out_dtype=torch.float32)
+        return ScaledSum.of(left, p.left_scale).plus(ScaledSum.of(right, p.right_scale))
 
 
 register_mixer("side_by_side", SideBySide)
