@@ -399,7 +399,7 @@ def main() -> int:
     ap.add_argument("--skip-decode", action="store_true", help="skip the decode measurement (profiling prefill)")
     ap.add_argument("--fast-fill", action="store_true",
                     help="profiling only: fill the cache pages with random values instead of prefilling the prompts")
-    ap.add_argument("--design", choices=["sinorax", "zeladra", "tanupel"], default=None,
+    ap.add_argument("--design", choices=["sinorax", "zeladra", "tanupel", "palulorn"], default=None,
                     help="instead of the benchmark: prefill and decode throughput of this design at a few sizes beside "
                          "a Llama-shaped model of equal size, and its kernels beside theirs (one JSON line)")
     ap.add_argument("--design-sizes", default="1b-like,3b-like", help="sizes of --design, with commas between them")

@@ -156,7 +156,9 @@ def _window_attention(dim: int, eps: float, m: Mapping[str, Any], prefix: str, w
         conv=int(m.get("conv") or 0),
     )
     names = {"wq": "q", "wk": "k", "wv": "v", "wo": "o", "bq": "q.b", "bk": "k.b", "bv": "v.b", "q_norm": "q.norm",
-             "k_norm": "k.norm", "conv_q": "q.conv", "conv_k": "k.conv", "conv_v": "v.conv"}
+             "k_norm": "k.norm"}
+    if params.conv:
+        names.update({"conv_q": "q.conv", "conv_k": "k.conv", "conv_v": "v.conv"})
     return PartSpec("gqa_attention", params, {k: prefix + v for k, v in names.items()})
 
 

@@ -510,7 +510,8 @@ extern "C" int fg_attention_prefill_tc5_bf16(const void* q, int q_stride, void* 
                                              int n_heads, int n_kv_heads, int head_dim, int window, float scale,
                                              unsigned int* work_counter, float* split_scratch, int* split_flags,
                                              int split_slots, int max_keys, const int* real_tiles, int nominal_tiles,
-                                             float softcap, int* status, cudaStream_t stream) {
+                                             float softcap, const float* sinks, int* status, cudaStream_t stream) {
+  // sinks: null, or float32 per query head: exp(sink_h) joins the softmax's denominator once
   if (n_tiles == 0) return 0;
   FG_CHECK_ARG(work_counter != nullptr, "fg_attention_prefill_tc5_bf16: no work counter");
   FG_CHECK_ARG(head_dim == FG_HEAD_DIM, "fg_attention_prefill_tc5_bf16: library built for head size %d, got %d",
@@ -554,7 +555,7 @@ extern "C" int fg_attention_prefill_tc5_bf16(const void* q, int q_stride, void* 
       km, vm, layer, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, block_table, table_width,
       page_size, n_pages, pos, tile_req, tile_tok0, tile_ntok, n_tiles, n_kv_heads, group, hpb, window,
       (capped ? softcap : scale) * 1.4426950408889634f, work_counter, parts, split_scratch, split_flags, split_slots,
-      real_tiles, status, nullptr, nullptr, nullptr, capped ? scale / softcap : 0.f);
+      real_tiles, status, sinks, nullptr, nullptr, capped ? scale / softcap : 0.f);
   FG_CHECK_LAUNCH("fg_attention_prefill_tc5_bf16");
   return 0;
 }

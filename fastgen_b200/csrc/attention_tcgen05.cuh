@@ -497,6 +497,14 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
         const uint32_t my_lane = (uint32_t)(warp * 32) << 16;  // this warp's quarter of the TMEM lanes
         float m_ref = -INFINITY, l_run = 0.f;
         const float c = scale_log2;
+        // softmax with sinks (`gate` then holds a sink per query head): exp(sink) joins the row's
+        // denominator once, without a key or a value: the reference maximum and the sum start from it
+        // (in the units of a raw score, which is multiplied by c).  Of a split item only the first
+        // part holds the sink.
+        if (!SIGMOID && gate != nullptr && my_valid && (!split || part == 0)) {
+          m_ref = gate[g * group + row_head(tid)] * 1.4426950408889634f / c;
+          l_run = 1.f;
+        }
         // sigmoid weights, in base 2: the row's gate and distance numbers
         float gate_l2 = 0.f, r1_row = 0.f, r2_row = 0.f;
         if (SIGMOID && my_valid) {

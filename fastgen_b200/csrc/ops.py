@@ -97,7 +97,7 @@ _ATTN_SIGNATURES = {
     "fg_attention_prefill_tma_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I,
                                       _I, _F, _I, _P, _P],
     "fg_attention_prefill_tc5_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I,
-                                      _I, _F, _P, _P, _P, _I, _I, _P, _I, _F, _P, _P],
+                                      _I, _F, _P, _P, _P, _I, _I, _P, _I, _F, _P, _P, _P],
     "fg_attention_prefill_tc5_split_slots": [_I, _I, _I, _I, _I],
     "fg_attention_decode_tma_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I,
                                      _F, _P, ctypes.c_longlong, _I, ctypes.c_longlong, _P, _P, _P, _P],
@@ -1181,12 +1181,12 @@ class Ops:
         # positions before those of the window
         # capped scores: the cap lives in the tcgen05 kernel (head sizes 64 and 128) and in the
         # mma.sync kernels on cp.async tiles
-        # sinks: prompt portions run on the mma.sync kernel on cp.async tiles, whose rows start their
-        # running maximum and sum from the sink; single tokens keep their kernels (the sink joins where
-        # the splits are merged)
+        # sinks: in prompt portions a row starts its running maximum and sum from the sink, in the
+        # tcgen05 kernel (head sizes 64 and 128) and in the mma.sync kernel on cp.async tiles; single
+        # tokens keep their kernels (the sink joins where the splits are merged)
         tc5 = head_dim in (64, 128) and self.use_tcgen05 and not keep_first
         use_tma = memory.tensor_maps is not None and (not softcap or tc5)
-        prompt_tma = use_tma and sinks is None
+        prompt_tma = use_tma and (sinks is None or tc5)
         rows = PREFILL_TMA_ROWS if prompt_tma else PREFILL_ROWS
         tiling = attention_tiling(n_heads, n_kv_heads, rows)
         tiles = ctx.attention_tiles(tiling, 2)
@@ -1205,7 +1205,7 @@ class Ops:
                 scratch, flags, room = self._split_buffers(head_dim, want)
                 _check(lib, lib.fg_attention_prefill_tc5_bf16(
                     *args, _ptr(self._work_counter), _ptr(scratch), _ptr(flags), room, max_keys,
-                    _ptr(tiles.count), nominal, float(softcap or 0.0), _ptr(self.status), _stream()))
+                    _ptr(tiles.count), nominal, float(softcap or 0.0), _ptr(sinks), _ptr(self.status), _stream()))
             else:
                 _check(lib, lib.fg_attention_prefill_tma_bf16(*args, keep_first, _ptr(self.status), _stream()))
         elif tiles.n:

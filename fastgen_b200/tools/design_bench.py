@@ -1,6 +1,6 @@
 """Throughput of one design beside another at equal size, step by step and kernel by kernel.
 
-``bench.py --design sinorax|zeladra|tanupel`` runs this: prefill and decode throughput of a model of that
+``bench.py --design sinorax|zeladra|tanupel|palulorn`` runs this: prefill and decode throughput of a model of that
 design at a few sizes that resemble a real model's layers (random weights), beside a Llama-shaped model of
 the same width, heads, head size, number of layers and number of parameters a layer, and the
 time of each kernel family of the two designs at those sizes with its fraction of the roofline
@@ -102,6 +102,29 @@ def tanupel_config(width, layers, heads, kv, head_dim, ffn, vocab, window=None, 
         out.append(dict(type=kind, mixer=dict(pair if kind == "parallel" else att), mlp=dict(dense if (i // 2) % 2 == 0 else routed)))
     return dict(architecture="Tanupel", vocab=vocab, width=width, norm=dict(eps=1e-5), embedding=dict(scale=1.0),
                 residual_mult=0.5, loop=dict(start=0, stop=layers, times=1), layers=out)
+
+
+def palulorn_config(width, layers, heads, kv, head_dim, ffn, vocab, window=1024, experts=8, top=2) -> dict:
+    """A pair of mixers (attention with a sink, whose values are its keys, with half the heads beside a
+    matrix memory with the other half), windowed attention with a short convolution and a norm per head,
+    and the gated linear recurrent unit, in turn; every feed-forward is routed: ``experts`` ungated
+    experts of ``3 ffn / (2 experts)`` rows with a squared ReLU (together the parameters of the Llama
+    shape's gated feed-forward, ``top`` of them a token, chosen among the best half of four groups) and a
+    shared expert of that size.  All layers are one run that is passed once, so the pass opens by mixing
+    the embedding output in and adding its step vector."""
+    left = dict(heads=heads // 2, kv_heads=max(1, kv // 2), dim=head_dim, vdim=head_dim, scale=head_dim ** -0.5,
+                q_temp=dict(coef=0.1, every=256))
+    right = dict(heads=heads // 2, dim=head_dim, vdim=head_dim, gate_cap=15.0)
+    att = dict(heads=heads, kv_heads=kv, dim=head_dim, vdim=head_dim, scale=head_dim ** -0.5, conv=4,
+               rot=dict(dims=head_dim // 2, base=500000.0, scaling=dict(factor=4.0)), mask=dict(size=window))
+    lru = dict(width=width, blocks=16, conv=4)
+    f = ffn * 3 // 2 // experts
+    routed = dict(kind="moe", expert=dict(ff=f), router=dict(experts=experts, top=top, scale=1.0, groups=dict(count=4, keep=2)),
+                  shared=dict(ff=f))
+    mixers = (("parallel", dict(left=left, right=right)), ("attention", att), ("rglru", lru))
+    out = [dict(type=mixers[i % 3][0], mixer=dict(mixers[i % 3][1]), mlp=dict(routed)) for i in range(layers)]
+    return dict(architecture="Palulorn", vocab=vocab, width=width, norm=dict(eps=1e-5), embedding=dict(scale=1.0),
+                loop=dict(start=0, stop=layers, times=1), layers=out)
 
 
 class Timer:
@@ -655,9 +678,188 @@ def tanupel_kernel_table(size, device, peaks) -> Dict[str, dict]:
     return table
 
 
+def palulorn_kernel_table(size, device, peaks) -> Dict[str, dict]:
+    """The kernels of the Palulorn design alone at one size, each beside the like kernel of the closest
+    model where there is one (Tanupel's delta rule for the matrix memory, its routed experts, the Llama
+    shape's attention and norm): microseconds and the fraction of the roofline."""
+    from ..csrc.ops import Ops
+    from ..engine.step import StepContext
+
+    width, _layers, heads, kv, head_dim, ffn, vocab, window = size
+    ops = Ops(torch.bfloat16, device)
+    timer = Timer(device)
+    gen = torch.Generator().manual_seed(SEED)
+    hbm, tensor = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    table: Dict[str, dict] = {}
+
+    def bw(name, us, nbytes):
+        table[name] = dict(us=round(us, 1), gbs=round(nbytes / (us * 1e-6) / 1e9, 1), hbm_frac=round(nbytes / (us * 1e-6) / hbm, 3))
+
+    def rand(*shape, dtype=torch.bfloat16):
+        return torch.randn(*shape, generator=gen).to(device, dtype)
+
+    def context(t, n_seqs):
+        ctx = StepContext(device)
+        per = t // n_seqs
+        ctx.req = torch.arange(n_seqs, dtype=torch.int32, device=device).repeat_interleave(per)
+        ctx.pos = torch.arange(t, dtype=torch.int32, device=device) % per + (DECODE_CONTEXT if n_seqs > 1 else 0)
+        ctx.seq_slot = torch.arange(n_seqs, dtype=torch.int32, device=device)
+        ctx.seq_start = torch.arange(0, t + 1, per, dtype=torch.int32, device=device)
+        ctx.n_tokens, ctx.n_seqs = t, n_seqs
+        return ctx
+
+    few = lambda t: t == DECODE_BATCH  # few tokens: time the captured launches (device time, not the host's)
+    cfg = palulorn_config(*size)
+    left, right = cfg["layers"][0]["mixer"]["left"], cfg["layers"][0]["mixer"]["right"]
+    att, lru = cfg["layers"][1]["mixer"], cfg["layers"][2]["mixer"]
+    for t in (PREFILL_TOKENS, DECODE_BATCH):
+        h = rand(t, width, dtype=torch.float32)
+        out = torch.empty(t, width, dtype=torch.bfloat16, device=device)
+        out32 = torch.empty(t, width, dtype=torch.float32, device=device)
+        y, wb = rand(t, width), rand(width)
+        bw(f"norm t={t}: rmsnorm of a half's output over the width (16-bit in, 32-bit out; twice a pair)",
+           timer.us(lambda: ops.rmsnorm(y, wb, 1e-5, out=out32), graph=few(t)), t * width * (2 + 4))
+        terms = [(rand(t, width, dtype=torch.float32), 0.5), (rand(t, width, dtype=torch.float32), 0.5)]
+        bw(f"norm+sum t={t}: rmsnorm of a sum (the pair's two normed outputs with factors, sum, norm)",
+           timer.us(lambda: ops.rmsnorm_sum(h, terms, wb, 1e-5, out=out), graph=few(t)), t * width * (4 + 4 + 2 * 4 + 2))
+        delta = rand(t, width)
+        bw(f"norm+sum t={t}: rmsnorm (sum, norm; llama)", timer.us(lambda: ops.rmsnorm(h, wb, 1e-5, out=out, delta=delta), graph=few(t)),
+           t * width * (4 + 4 + 2 + 2))
+        bw(f"pass input t={t}: sum and rounding of the stream before the map",
+           timer.us(lambda: ops.rmsnorm_sum(h, [(delta, 1.0)], None, 0.0, out=out), graph=few(t)), t * width * (4 + 4 + 2 + 2))
+        ctx = context(t, 1 if t > DECODE_BATCH else DECODE_BATCH)
+        q, k = rand(t, att["heads"] * head_dim), rand(t, att["kv_heads"] * head_dim)
+        bw(f"query/key norm t={t}: a factor per (token, head)",
+           timer.us(lambda: ops.qk_head_factors(q, k, ctx.pos, ctx.req, att["heads"], att["kv_heads"], head_dim, head_dim, 1e-5),
+                    graph=few(t)), t * (q.shape[1] + k.shape[1]) * 2)
+        o, gate = rand(t, left["heads"] * head_dim), rand(t, left["heads"])
+        bw(f"head gate t={t}: a head's output times its sigmoid gate, in place",
+           timer.us(lambda: ops.head_gate(o, gate, ctx.req, left["heads"], head_dim), graph=few(t)), t * o.shape[1] * 4)
+
+    # the matrix memory's kernels, beside the delta rule's of Tanupel at the same heads and state
+    H, d, dv = right["heads"], right["dim"], right["vdim"]
+    floats = ops.mlstm_state_floats(H, d, dv)
+    bias, norm_w = rand(2 * H, dtype=torch.float32), rand(H * dv, dtype=torch.float32)
+    dr = tanupel_config(*size)["layers"][0]["mixer"]["right"]
+    G, taps = dr["kv_heads"], dr["conv"]
+    dch = 2 * G * d + H * dv
+    dstate = torch.zeros(DECODE_BATCH, H * dv * d + (taps - 1) * dch, dtype=torch.float32, device=device)
+    dt_bias, a_log = rand(H * d, dtype=torch.float32), rand(H, dtype=torch.float32)
+    for t, n_seqs in ((PREFILL_TOKENS, 1), (DECODE_BATCH, DECODE_BATCH)):
+        ctx = context(t, n_seqs)
+        state = torch.zeros(DECODE_BATCH, floats, dtype=torch.float32, device=device)
+        q, k, v, z = rand(t, H * d), rand(t, H * d), rand(t, H * dv), rand(t, H * dv)
+        gates = rand(t, 2 * H, dtype=torch.float32)
+        run = lambda: ops.mlstm_scan(gates.clone(), bias, 15.0, q, k, v, state, ctx, H, d, dv, d ** -0.5)
+        nbytes = t * (2 * H * d + H * dv) * 2 + t * H * (dv + 1) * 4 + n_seqs * floats * 8
+        bw(f"matrix memory t={t}: gates, maxima, recurrence ({n_seqs} sequences, {H} heads, state {d} x {dv} + normaliser)",
+           timer.us(run, graph=few(t)), nbytes)
+        y, coef = run()
+        bw(f"matrix memory t={t}: division, norm per head, gate", timer.us(lambda: ops.mlstm_out(y, coef, z, norm_w, H, dv, 1e-5, ctx),
+                                                                        graph=few(t)), t * H * dv * (4 + 2 + 2))
+        qkv, a, b = rand(t, dch, dtype=torch.float32), rand(t, H * d), rand(t, H)
+        bw(f"delta rule (tanupel) t={t}: recurrence ({n_seqs} sequences, {H} heads, state {d} x {dv})", timer.us(lambda: ops.delta_scan(
+            qkv, a, b, dt_bias, a_log, dstate, ctx, H, G, d, dv), graph=few(t)), t * (dch * 4 + H * d * 2 + H * dv * 4) + n_seqs * H * dv * d * 8)
+        dstate.zero_()
+
+    # the gated linear recurrent unit
+    W, blocks, ltaps = lru["width"], lru["blocks"], lru["conv"]
+    bwid = W // blocks
+    br, bi, rate = rand(W, dtype=torch.float32), rand(W, dtype=torch.float32), -rand(W, dtype=torch.float32).abs()
+    conv_w, conv_b = rand(W, ltaps, dtype=torch.float32), rand(W, dtype=torch.float32)
+    w_gates_t = rand(blocks, bwid, 2 * bwid)
+    for t, n_seqs in ((PREFILL_TOKENS, 1), (DECODE_BATCH, DECODE_BATCH)):
+        ctx = context(t, n_seqs)
+        state = torch.zeros(DECODE_BATCH, W + (ltaps - 1) * W, dtype=torch.float32, device=device)
+        xb, yb = rand(t, W), rand(t, W)
+        bw(f"recurrent unit t={t}: convolution with bias", timer.us(lambda: ops.time_conv(
+            xb, 0, W, conv_w, conv_b, state, W, ltaps, ctx, out_dtype=torch.bfloat16), graph=few(t)), t * W * (2 + 2))
+        u = ops.time_conv(xb, 0, W, conv_w, conv_b, state, W, ltaps, ctx, out_dtype=torch.bfloat16)
+        us = timer.us(lambda: ops.block_products(u.view(t, blocks, bwid), w_gates_t, None), graph=few(t))
+        table[f"recurrent unit t={t}: block-diagonal gate maps ({blocks} blocks of {bwid}; the library's batched product)"] = dict(
+            us=round(us, 1), tflops=round(4 * t * W * bwid / (us * 1e-6) / 1e12, 1))
+        gates = ops.block_products(u.view(t, blocks, bwid), w_gates_t, None)
+        bw(f"recurrent unit t={t}: coefficients and chain ({n_seqs} sequences, {W} channels)", timer.us(lambda: ops.rglru_scan(
+            gates, u, br, bi, rate, yb, state, 0, ctx, blocks), graph=few(t)), t * W * (8 + 2 + 8 + 8 + 2 + 2))
+
+    # routed experts without a gate beside Tanupel's gated ones of as many parameters
+    mlp = cfg["layers"][0]["mlp"]
+    E, top, f = mlp["router"]["experts"], mlp["router"]["top"], mlp["expert"]["ff"]
+    groups = (mlp["router"]["groups"]["count"], mlp["router"]["groups"]["keep"], 2)
+    w_up, w_down = rand(E, f, width), rand(E, width, f)
+    tf = ffn // E
+    w13, w2 = rand(E, 2 * tf, width), rand(E, width, tf)
+    router = rand(E, width, dtype=torch.float32)
+    for t in (PREFILL_TOKENS, DECODE_BATCH):
+        x = rand(t, width)
+        ctx = context(t, 1)
+        logits = ops.moe_logits(x, router)
+        route = lambda: ops.moe_route(logits, None, top, ctx, renormalize=True, score="sigmoid", groups=groups, renorm_eps=1e-20,
+                                      weight_scale=1.5)
+        ids, weights = route()
+        row = dict(router_logits_us=round(timer.us(lambda: ops.moe_logits(x, router), graph=few(t)), 1),
+                   choice_us=round(timer.us(route, graph=few(t)), 1))
+        us = timer.us(lambda: ops.moe_experts(x, ids, weights, w_up, None, w_down, w_up, act="relu2"), graph=few(t))
+        flops = 4 * t * top * f * width
+        touched = min(E, t * top)
+        row.update(experts_us=round(us, 1), experts_tflops=round(flops / (us * 1e-6) / 1e12, 1),
+                   experts_tensor_frac=round(flops / (us * 1e-6) / tensor, 3),
+                   experts_hbm_frac=round(touched * 2 * f * width * 2 / (us * 1e-6) / hbm, 3))
+        table[f"routed experts t={t}: {top} of {E} ungated experts of {f} rows, squared ReLU"] = row
+        ids2, weights2 = ops.moe_route(logits, None, top, ctx)
+        us = timer.us(lambda: ops.moe_experts(x, ids2, weights2, w13[:, :tf], w13[:, tf:], w2, w13), graph=few(t))
+        flops = 6 * t * top * tf * width
+        table[f"routed experts (tanupel) t={t}: {top} of {E} gated experts of {tf} rows"] = dict(
+            choice_us=round(timer.us(lambda: ops.moe_route(logits, None, top, ctx), graph=few(t)), 1),
+            experts_us=round(us, 1), experts_tflops=round(flops / (us * 1e-6) / 1e12, 1),
+            experts_tensor_frac=round(flops / (us * 1e-6) / tensor, 3),
+            experts_hbm_frac=round(touched * 3 * tf * width * 2 / (us * 1e-6) / hbm, 3))
+
+    small = (width, 3, heads, kv, head_dim, ffn, 1024)
+    pz = palulorn_config(*small, window)
+    table["attention softmax with a sink, values = keys (palulorn pair's left half, causal)"] = _attention_times(
+        pz, device, timer, 0, None, left["heads"], left["kv_heads"], head_dim, pick=lambda m: m.left)
+    table[f"attention softmax (palulorn 'attention', window {window})"] = _attention_times(pz, device, timer, 1, window, heads, kv, head_dim)
+    table["attention softmax (llama, causal)"] = _attention_times(llama_config(*small), device, timer, 0, None, heads, kv, head_dim)
+    table[f"attention softmax (llama, window {window})"] = _attention_times(llama_config(*small, window=window), device, timer, 0,
+                                                                          window, heads, kv, head_dim)
+    for name, row in table.items():
+        if "prefill_tflops" in row:
+            row["prefill_tensor_frac"] = round(row["prefill_tflops"] * 1e12 / tensor, 3)
+            row["decode_hbm_frac"] = round(row["decode_gbs"] * 1e9 / hbm, 3)
+    # whole mixers (projections included)
+    table["mixer pair (palulorn: attention with a sink beside the matrix memory, both normed; whole mixer)"] = _mixer_times(pz, device, timer, 0)
+    table["mixer pair's left half alone (palulorn; whole mixer)"] = _mixer_times(pz, device, timer, 0, pick=lambda b: b.mixer.left)
+    table["mixer pair's right half alone (palulorn matrix memory; whole mixer)"] = _mixer_times(pz, device, timer, 0, pick=lambda b: b.mixer.right)
+    table["mixer attention (palulorn: convolution, norm per head, window; whole mixer)"] = _mixer_times(pz, device, timer, 1)
+    table["mixer recurrent unit (palulorn; whole mixer)"] = _mixer_times(pz, device, timer, 2)
+    table["feed-forward (palulorn: routed and shared experts; whole)"] = _mixer_times(pz, device, timer, 0, pick=lambda b: b.ffn)
+    tz = tanupel_config(width, 2, heads, kv, head_dim, ffn, 1024)
+    table["mixer pair (tanupel: capped attention beside the delta rule; whole mixer)"] = _mixer_times(tz, device, timer, 0)
+    table["mixer attention (llama, causal; whole mixer)"] = _mixer_times(llama_config(*small), device, timer, 0)
+    return table
+
+
 def run(sizes: List[str], peaks: dict, kernels: bool = True, design: str = "sinorax") -> dict:
     device = torch.device("cuda:0")
     torch.cuda.set_device(device)
+    if design == "palulorn":
+        out = {"metric": "prefill and decode tokens/s of Palulorn beside Tanupel and a Llama-shaped model of equal size (bf16, random weights)",
+               "unit": "tokens/s", "dtype": "bf16", "data": "synthetic (random weights, uniform random token ids)",
+               "config": dict(prefill_tokens=PREFILL_TOKENS, decode_batch=DECODE_BATCH, decode_context=DECODE_CONTEXT, page=PAGE,
+                              l2="flushed before every timed kernel; model steps stream all weights"),
+               "peaks": peaks, "sizes": {}}
+        for name in sizes:
+            size = SIZES[name]
+            entry = dict(width=size[0], layers=size[1], heads=size[2], kv_heads=size[3], head_dim=size[4], swiglu_ffn=size[5],
+                         vocab=size[6], window=size[7], experts=8, top=2, expert_ffn=size[5] * 3 // 2 // 8)
+            entry["palulorn"] = model_throughput(palulorn_config(*size), device)
+            entry["tanupel"] = model_throughput(tanupel_config(*size), device)
+            entry["llama"] = model_throughput(llama_config(*size[:7]), device)
+            if kernels:
+                entry["kernels"] = palulorn_kernel_table(size, device, peaks)
+            out["sizes"][name] = entry
+        return out
     if design == "tanupel":
         out = {"metric": "prefill and decode tokens/s of Tanupel beside a Llama-shaped model of equal size (bf16, random weights)",
                "unit": "tokens/s", "dtype": "bf16", "data": "synthetic (random weights, uniform random token ids)",
