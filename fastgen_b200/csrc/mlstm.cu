@@ -16,12 +16,36 @@
 // slot (seq_slot < 0: padding that touches nothing).
 //
 // Three kernels: the gates of every token side by side (nothing here depends on the state), the chain
-// of running maxima (an addition and a maximum a token), and the recurrence itself, which runs token
+// of running maxima (an addition and a maximum a token, fed from shared memory), and the recurrence itself, which runs token
 // by token so that its sums do not depend on how a prompt was cut or on what else is in the batch.
 // A fourth divides, norms per head and gates the read-out.
 #include "common.cuh"
 
 namespace {
+
+// The values of one 16-byte piece of a row.
+template <typename T>
+struct Piece;
+template <>
+struct Piece<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void unpack(const uint4& raw, float (&v)[4]) {
+    v[0] = __uint_as_float(raw.x); v[1] = __uint_as_float(raw.y); v[2] = __uint_as_float(raw.z); v[3] = __uint_as_float(raw.w);
+  }
+};
+template <>
+struct Piece<__nv_bfloat16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void unpack(const uint4& raw, float (&v)[8]) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(h[i]);
+      v[2 * i] = f.x;
+      v[2 * i + 1] = f.y;
+    }
+  }
+};
 
 __device__ __forceinline__ float log_sigmoid(float z) {
   // -softplus(-z), exact at both ends
@@ -42,72 +66,94 @@ __global__ void mlstm_gates_kernel(float* __restrict__ gates, const float* __res
 }
 
 // ---- the chain of running maxima ------------------------------------------------------------------
-// A thread a (sequence, head).  coef[t, h] = (f + m - m', i - m', -m'): the logarithms of what the
-// recurrence multiplies S by, multiplies k v^T by, and of the floor of the denominator.
-__global__ void mlstm_maxima_kernel(const float* __restrict__ gates, float* __restrict__ coef,
-                                    float* __restrict__ state, long state_stride, long m_offset,
-                                    const int* __restrict__ seq_slot, const int* __restrict__ seq_start, int n_seqs,
-                                    int heads) {
-  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= n_seqs * heads) return;
-  const int s = idx / heads, h = idx % heads;
+// A block a sequence.  A stretch of tokens' gates comes into shared memory side by side (one contiguous
+// run of global memory), thread h walks head h's chain over the stretch, and the stretch's coefficients
+// leave side by side: the chain itself never waits for global memory.
+// coef[t, h] = (f + m - m', i - m', -m'): the logarithms of what the recurrence multiplies S by, multiplies
+// k v^T by, and of the floor of the denominator.
+constexpr int MX_THREADS = 128;
+
+__global__ void __launch_bounds__(MX_THREADS)
+mlstm_maxima_kernel(const float* __restrict__ gates, float* __restrict__ coef, float* __restrict__ state,
+                    long state_stride, long m_offset, const int* __restrict__ seq_slot,
+                    const int* __restrict__ seq_start, int heads, int stretch) {
+  extern __shared__ float mx_smem[];
+  float* g = mx_smem;                        // [stretch][2 heads]
+  float* c = g + (size_t)stretch * 2 * heads;  // [stretch][heads][3]
+  const int s = blockIdx.x, tid = threadIdx.x;
   const int slot = seq_slot[s];
   if (slot < 0) return;
   const int t0 = seq_start[s], t1 = seq_start[s + 1];
-  float* mp = state + (size_t)slot * state_stride + m_offset + h;
-  float m = *mp;
-  constexpr int U = 8;
-  for (int t = t0; t < t1; t += U) {
-    float gi[U], gf[U];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int tt = min(t + u, t1 - 1);
-      gi[u] = gates[(size_t)tt * 2 * heads + h];
-      gf[u] = gates[(size_t)tt * 2 * heads + heads + h];
+  float* mp = state + (size_t)slot * state_stride + m_offset;
+  // (more heads than threads: a thread walks several chains)
+  for (int h0 = 0; h0 < heads; h0 += MX_THREADS) {
+    const int h = h0 + tid;
+    float m = h < heads ? mp[h] : 0.f;
+    for (int ts = t0; ts < t1; ts += stretch) {
+      const int nt = min(stretch, t1 - ts);
+      __syncthreads();
+      for (int i = tid; i < nt * 2 * heads; i += MX_THREADS) g[i] = gates[(size_t)ts * 2 * heads + i];
+      __syncthreads();
+      if (h < heads) {
+        for (int tt = 0; tt < nt; ++tt) {
+          const float gi = g[tt * 2 * heads + h], gf = g[tt * 2 * heads + heads + h];
+          const float mn = fmaxf(gf + m, gi);
+          float* o = c + ((size_t)tt * heads + h) * 3;
+          o[0] = gf + m - mn;
+          o[1] = gi - mn;
+          o[2] = -mn;
+          m = mn;
+        }
+      }
+      __syncthreads();
+      if (h0 == 0 && heads <= MX_THREADS) {
+        for (int i = tid; i < nt * 3 * heads; i += MX_THREADS) coef[(size_t)ts * 3 * heads + i] = c[i];
+      } else {
+        for (int i = tid; i < nt * 3 * heads; i += MX_THREADS) {
+          const int hh = (i / 3) % heads;
+          if (hh >= h0 && hh < h0 + MX_THREADS) coef[(size_t)ts * 3 * heads + i] = c[i];
+        }
+      }
     }
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      if (t + u >= t1) break;
-      const float mn = fmaxf(gf[u] + m, gi[u]);
-      float* c = coef + ((size_t)(t + u) * heads + h) * 3;
-      c[0] = gf[u] + m - mn;
-      c[1] = gi[u] - mn;
-      c[2] = -mn;
-      m = mn;
-    }
+    if (h < heads) mp[h] = m;
   }
-  *mp = m;
 }
 
 // ---- the recurrence ---------------------------------------------------------------------------------
 // A block works on (sequence, head, MS_COLS columns of dv + 1); MS_LANES threads share a column, each
 // with every MS_LANES-th row of the state in registers (NPT rows a thread; rows beyond d are zero and
-// meet zero q and k).  Tokens are staged through shared memory 32 (large heads: 8) at a time.
+// meet zero q and k).  Tokens are staged through shared memory in two buffers: while the block's four
+// computing warps walk a stage, its two fetching warps bring the next one (q times its scale, k, the
+// values times exp(i - m'), the decays exp(f + m - m')), so the chain does not wait for global memory.
 constexpr int MS_COLS = 16;
 constexpr int MS_LANES = 8;
-constexpr int MS_THREADS = MS_COLS * MS_LANES;
+constexpr int MS_COMPUTE = MS_COLS * MS_LANES;
+constexpr int MS_FETCH = 64;
+constexpr int MS_THREADS = MS_COMPUTE + MS_FETCH;
 
 template <typename T, int NPT>
 __global__ void __launch_bounds__(MS_THREADS)
 mlstm_scan_kernel(const T* __restrict__ q, long q_stride, const T* __restrict__ k, long k_stride,
                   const T* __restrict__ v, long v_stride, const float* __restrict__ coef, float* __restrict__ y,
                   long y_stride, float* __restrict__ state, long state_stride, const int* __restrict__ seq_slot,
-                  const int* __restrict__ seq_start, int heads, int d, int dv, float q_scale) {
-  constexpr int DP = NPT * MS_LANES;  // padded rows
-  constexpr int MS_TOKENS = NPT > 16 ? 8 : 32;  // tokens a stage: the stage's q and k fit 32 KiB
-  __shared__ float qs[MS_TOKENS][DP];
-  __shared__ float ks[MS_TOKENS][DP];
-  __shared__ float vs[MS_TOKENS][MS_COLS];  // value times exp(i - m')
-  __shared__ float keep[MS_TOKENS];
-  __shared__ float ys[MS_TOKENS][MS_COLS];
+                  const int* __restrict__ seq_start, int heads, int d, int dv, float q_scale, bool vec) {
+  // vec: the rows of q and k can be read in 16-byte pieces (the launch has checked sizes and alignment)
+  constexpr int DP = NPT * MS_LANES;                        // padded rows
+  constexpr int MS_TOKENS = DP >= 64 ? 2048 / DP : 32;      // tokens a stage: two stages of q and k fit 32 KiB
+  __shared__ float qs[2][MS_TOKENS][DP];
+  __shared__ float ks[2][MS_TOKENS][DP];
+  __shared__ float vs[2][MS_TOKENS][MS_COLS];  // value times exp(i - m')
+  __shared__ float keep[2][MS_TOKENS];
+  __shared__ float ys[2][MS_TOKENS][MS_COLS];
   const int s = blockIdx.z, h = blockIdx.y, c0 = blockIdx.x * MS_COLS;
   const int slot = seq_slot[s];
   if (slot < 0) return;
   const int t0 = seq_start[s], t1 = seq_start[s + 1];
   if (t1 <= t0) return;
   const int tid = threadIdx.x, lane = tid % MS_LANES, cl = tid / MS_LANES;
+  const bool computes = tid < MS_COMPUTE;
   const int col = c0 + cl;
-  const bool live = col <= dv;  // column dv is n
+  const bool live = computes && col <= dv;  // column dv is n
   float* sp = state + (size_t)slot * state_stride + ((size_t)h * (dv + 1) + min(col, dv)) * d;
   float S[NPT];
 #pragma unroll
@@ -115,46 +161,100 @@ mlstm_scan_kernel(const T* __restrict__ q, long q_stride, const T* __restrict__ 
     const int r = lane + MS_LANES * i;
     S[i] = (live && r < d) ? sp[r] : 0.f;
   }
-  for (int ts = t0; ts < t1; ts += MS_TOKENS) {
-    const int nt = min(MS_TOKENS, t1 - ts);
-    __syncthreads();  // the stage before has been read
-    for (int i = tid; i < nt * DP; i += MS_THREADS) {
-      const int tt = i / DP, r = i - tt * DP;
-      float qv = 0.f, kv = 0.f;
-      if (r < d) {
-        qv = to_f32<T>(q[(size_t)(ts + tt) * q_stride + (size_t)h * d + r]) * q_scale;
-        kv = to_f32<T>(k[(size_t)(ts + tt) * k_stride + (size_t)h * d + r]);
-      }
-      qs[tt][r] = qv;
-      ks[tt][r] = kv;
+  const int n_stages = (t1 - t0 + MS_TOKENS - 1) / MS_TOKENS;
+  if (vec) {
+    // the pieces never reach the rows beyond d: those are zero for good
+    for (int i = tid; i < 2 * MS_TOKENS * DP; i += MS_THREADS) {
+      (&qs[0][0][0])[i] = 0.f;
+      (&ks[0][0][0])[i] = 0.f;
     }
-    for (int i = tid; i < nt * MS_COLS; i += MS_THREADS) {
+    __syncthreads();
+  }
+  auto fetch = [&](int stage, int first, int step) {
+    const int ts = t0 + stage * MS_TOKENS, nt = min(MS_TOKENS, t1 - ts), buf = stage & 1;
+    if (vec) {
+      // 16-byte pieces, four of q and four of k in flight a thread before any is unpacked
+      constexpr int VE = Piece<T>::N;
+      const int cpr = d / VE, n = nt * cpr;
+      for (int base = first; base < n; base += 4 * step) {
+        uint4 qa[4], ka[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int i = base + u * step;
+          if (i < n) {
+            const int tt = i / cpr, r0 = (i - tt * cpr) * VE;
+            qa[u] = *reinterpret_cast<const uint4*>(q + (size_t)(ts + tt) * q_stride + (size_t)h * d + r0);
+            ka[u] = *reinterpret_cast<const uint4*>(k + (size_t)(ts + tt) * k_stride + (size_t)h * d + r0);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int i = base + u * step;
+          if (i < n) {
+            const int tt = i / cpr, r0 = (i - tt * cpr) * VE;
+            float qv[VE], kv[VE];
+            Piece<T>::unpack(qa[u], qv);
+            Piece<T>::unpack(ka[u], kv);
+#pragma unroll
+            for (int j = 0; j < VE; ++j) {
+              qs[buf][tt][r0 + j] = qv[j] * q_scale;
+              ks[buf][tt][r0 + j] = kv[j];
+            }
+          }
+        }
+      }
+    } else {
+#pragma unroll 4
+      for (int i = first; i < nt * DP; i += step) {
+        const int tt = i / DP, r = i - tt * DP;
+        float qv = 0.f, kv = 0.f;
+        if (r < d) {
+          qv = to_f32<T>(q[(size_t)(ts + tt) * q_stride + (size_t)h * d + r]) * q_scale;
+          kv = to_f32<T>(k[(size_t)(ts + tt) * k_stride + (size_t)h * d + r]);
+        }
+        qs[buf][tt][r] = qv;
+        ks[buf][tt][r] = kv;
+      }
+    }
+    for (int i = first; i < nt * MS_COLS; i += step) {
       const int tt = i / MS_COLS, c = c0 + (i - tt * MS_COLS);
       const float w = expf(coef[((size_t)(ts + tt) * heads + h) * 3 + 1]);
       float vv = 0.f;
       if (c < dv) vv = to_f32<T>(v[(size_t)(ts + tt) * v_stride + (size_t)h * dv + c]) * w;
       else if (c == dv) vv = w;
-      vs[tt][i - tt * MS_COLS] = vv;
+      vs[buf][tt][i - tt * MS_COLS] = vv;
     }
-    for (int i = tid; i < nt; i += MS_THREADS) keep[i] = expf(coef[((size_t)(ts + i) * heads + h) * 3]);
-    __syncthreads();
-    for (int tt = 0; tt < nt; ++tt) {
-      const float kp = keep[tt], vv = vs[tt][cl];
-      float acc = 0.f;
+    for (int i = first; i < nt; i += step) keep[buf][i] = expf(coef[((size_t)(ts + i) * heads + h) * 3]);
+  };
+  fetch(0, tid, MS_THREADS);
+  __syncthreads();
+  for (int stage = 0; stage < n_stages; ++stage) {
+    const int ts = t0 + stage * MS_TOKENS, nt = min(MS_TOKENS, t1 - ts), buf = stage & 1;
+    if (computes) {
+      for (int tt = 0; tt < nt; ++tt) {
+        const float kp = keep[buf][tt], vv = vs[buf][tt][cl];
+        float acc0 = 0.f, acc1 = 0.f;
 #pragma unroll
-      for (int i = 0; i < NPT; ++i) {
-        S[i] = fmaf(kp, S[i], ks[tt][lane + MS_LANES * i] * vv);
-        acc = fmaf(S[i], qs[tt][lane + MS_LANES * i], acc);
+        for (int i = 0; i < NPT; i += 2) {
+          S[i] = fmaf(kp, S[i], ks[buf][tt][lane + MS_LANES * i] * vv);
+          acc0 = fmaf(S[i], qs[buf][tt][lane + MS_LANES * i], acc0);
+          S[i + 1] = fmaf(kp, S[i + 1], ks[buf][tt][lane + MS_LANES * (i + 1)] * vv);
+          acc1 = fmaf(S[i + 1], qs[buf][tt][lane + MS_LANES * (i + 1)], acc1);
+        }
+        float acc = acc0 + acc1;
+        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+        if (lane == 0) ys[buf][tt][cl] = acc;
       }
-      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-      if (lane == 0) ys[tt][cl] = acc;
+    } else if (stage + 1 < n_stages) {
+      fetch(stage + 1, tid - MS_COMPUTE, MS_FETCH);
     }
     __syncthreads();
+    // (this stage's outputs leave while the next stage is walked: they have a buffer of their own)
     for (int i = tid; i < nt * MS_COLS; i += MS_THREADS) {
       const int tt = i / MS_COLS, c = c0 + (i - tt * MS_COLS);
-      if (c <= dv) y[(size_t)(ts + tt) * y_stride + (size_t)h * (dv + 1) + c] = ys[tt][i - tt * MS_COLS];
+      if (c <= dv) y[(size_t)(ts + tt) * y_stride + (size_t)h * (dv + 1) + c] = ys[buf][tt][i - tt * MS_COLS];
     }
   }
   if (live) {
@@ -199,9 +299,11 @@ int launch_scan(const T* q, long qs, const T* k, long ks, const T* v, long vs, c
                 float* state, long ss, const int* seq_slot, const int* seq_start, int n_seqs, int heads, int d, int dv,
                 float q_scale, cudaStream_t stream) {
   const dim3 grid((dv + 1 + MS_COLS - 1) / MS_COLS, heads, n_seqs);
+  constexpr int VE = 16 / (int)sizeof(T);
+  const bool vec = d % VE == 0 && qs % VE == 0 && ks % VE == 0 && ((uintptr_t)q & 15) == 0 && ((uintptr_t)k & 15) == 0;
 #define FG_MS(NPT)                                                                                                  \
   mlstm_scan_kernel<T, NPT><<<grid, MS_THREADS, 0, stream>>>(q, qs, k, ks, v, vs, coef, y, ys, state, ss, seq_slot, \
-                                                             seq_start, heads, d, dv, q_scale)
+                                                             seq_start, heads, d, dv, q_scale, vec)
   if (d <= 32) FG_MS(4);
   else if (d <= 64) FG_MS(8);
   else if (d <= 128) FG_MS(16);
@@ -229,8 +331,12 @@ extern "C" int fg_mlstm_scan(float* gates, const float* gate_bias, float cap, co
   mlstm_gates_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(gates, gate_bias, req, n_tokens, heads, cap);
   FG_CHECK_LAUNCH("fg_mlstm_scan (gates)");
   const long m_offset = (long)heads * (dv + 1) * d;
-  mlstm_maxima_kernel<<<(n_seqs * heads + 63) / 64, 64, 0, stream>>>(gates, coef, state, state_stride, m_offset,
-                                                                      seq_slot, seq_start, n_seqs, heads);
+  // a stretch of tokens whose gates and coefficients fit 40 KiB of shared memory
+  int stretch = (40 * 1024 / 4) / (5 * heads);
+  stretch = stretch < 1 ? 1 : (stretch > 256 ? 256 : stretch);
+  FG_CHECK_ARG(5 * heads * 4 <= 40 * 1024, "fg_mlstm_scan: %d heads are too many", heads);
+  mlstm_maxima_kernel<<<n_seqs, MX_THREADS, (size_t)stretch * 5 * heads * sizeof(float), stream>>>(
+      gates, coef, state, state_stride, m_offset, seq_slot, seq_start, heads, stretch);
   FG_CHECK_LAUNCH("fg_mlstm_scan (maxima)");
   if (dtype == FG_F32)
     return launch_scan((const float*)q, q_stride, (const float*)k, k_stride, (const float*)v, v_stride, coef, y,

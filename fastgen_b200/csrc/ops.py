@@ -1075,9 +1075,9 @@ class Ops:
         library's batched product with float32 results (``w_t`` [blocks, a, n]); float32 runs this
         package's float32 product block by block."""
         t, blocks, a = x.shape
-        n = w.shape[1]
         if x.dtype == torch.bfloat16:
             return torch.bmm(x.permute(1, 0, 2), w_t, out_dtype=torch.float32)
+        n = w.shape[1]
         out = torch.empty((blocks, t, n), dtype=torch.float32, device=x.device)
         for b in range(blocks):
             self.linear(x[:, b, :], w[b], out=out[b])
