@@ -55,14 +55,18 @@ __device__ __forceinline__ float log_sigmoid(float z) {
 // ---- gates ------------------------------------------------------------------------------------------
 // gates: float32 [T, 2 heads] raw sums (input gates, then forget gates), replaced in place by the
 // capped log gates i and f.
+__device__ __forceinline__ float log_gate(float raw, float bias, float cap, bool forget) {
+  const float z = cap * tanhf((raw + bias) / cap);
+  return forget ? log_sigmoid(z) : z;
+}
+
 __global__ void mlstm_gates_kernel(float* __restrict__ gates, const float* __restrict__ bias,
                                    const int* __restrict__ req, int n_tokens, int heads, float cap) {
   const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (long)n_tokens * 2 * heads) return;
   const int t = (int)(idx / (2 * heads)), j = (int)(idx % (2 * heads));
   if (req[t] < 0) return;
-  const float z = cap * tanhf((gates[idx] + bias[j]) / cap);
-  gates[idx] = j < heads ? z : log_sigmoid(z);
+  gates[idx] = log_gate(gates[idx], bias[j], cap, j >= heads);
 }
 
 // ---- the chain of running maxima ------------------------------------------------------------------
@@ -76,7 +80,10 @@ constexpr int MX_THREADS = 128;
 __global__ void __launch_bounds__(MX_THREADS)
 mlstm_maxima_kernel(const float* __restrict__ gates, float* __restrict__ coef, float* __restrict__ state,
                     long state_stride, long m_offset, const int* __restrict__ seq_slot,
-                    const int* __restrict__ seq_start, int heads, int stretch) {
+                    const int* __restrict__ seq_start, int heads, int stretch, const float* __restrict__ raw_bias,
+                    float cap) {
+  // raw_bias: null, or the gates are still raw sums and become log gates on their way in (steps of a few
+  // tokens, which then need no kernel of their own for that)
   extern __shared__ float mx_smem[];
   float* g = mx_smem;                        // [stretch][2 heads]
   float* c = g + (size_t)stretch * 2 * heads;  // [stretch][heads][3]
@@ -92,7 +99,14 @@ mlstm_maxima_kernel(const float* __restrict__ gates, float* __restrict__ coef, f
     for (int ts = t0; ts < t1; ts += stretch) {
       const int nt = min(stretch, t1 - ts);
       __syncthreads();
-      for (int i = tid; i < nt * 2 * heads; i += MX_THREADS) g[i] = gates[(size_t)ts * 2 * heads + i];
+      for (int i = tid; i < nt * 2 * heads; i += MX_THREADS) {
+        float v = gates[(size_t)ts * 2 * heads + i];
+        if (raw_bias != nullptr) {
+          const int j = i % (2 * heads);
+          v = log_gate(v, raw_bias[j], cap, j >= heads);
+        }
+        g[i] = v;
+      }
       __syncthreads();
       if (h < heads) {
         for (int tt = 0; tt < nt; ++tt) {
@@ -317,7 +331,7 @@ int launch_scan(const T* q, long qs, const T* k, long ks, const T* v, long vs, c
 
 extern "C" long long fg_mlstm_state_floats(int heads, int d, int dv) { return (long long)heads * (dv + 1) * d + heads; }
 
-// gates: float32 [T, 2 heads] raw sums, overwritten with the log gates.  q, k, v: row-strided views of the
+// gates: float32 [T, 2 heads] raw sums (steps of many tokens overwrite them with the log gates).  q, k, v: row-strided views of the
 // compute type.  coef: float32 scratch [T, heads, 3].  y: float32 [T, heads * (dv + 1)].
 extern "C" int fg_mlstm_scan(float* gates, const float* gate_bias, float cap, const void* q, long q_stride, const void* k,
                              long k_stride, const void* v, long v_stride, int dtype, float* coef, float* y,
@@ -327,16 +341,20 @@ extern "C" int fg_mlstm_scan(float* gates, const float* gate_bias, float cap, co
   if (n_tokens == 0 || n_seqs == 0) return 0;
   FG_CHECK_ARG(heads > 0 && d > 0 && d <= 256 && dv > 0 && cap > 0.f, "fg_mlstm_scan: %d heads of %d x %d", heads, d, dv);
   FG_CHECK_ARG(n_seqs <= 65535 && heads <= 65535, "fg_mlstm_scan: too many sequences or heads");
-  const long n = (long)n_tokens * 2 * heads;
-  mlstm_gates_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(gates, gate_bias, req, n_tokens, heads, cap);
-  FG_CHECK_LAUNCH("fg_mlstm_scan (gates)");
+  // many tokens: the gates of all tokens side by side first; few: on their way into the chain's kernel
+  const bool few = n_tokens <= 4 * n_seqs;
+  if (!few) {
+    const long n = (long)n_tokens * 2 * heads;
+    mlstm_gates_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(gates, gate_bias, req, n_tokens, heads, cap);
+    FG_CHECK_LAUNCH("fg_mlstm_scan (gates)");
+  }
   const long m_offset = (long)heads * (dv + 1) * d;
   // a stretch of tokens whose gates and coefficients fit 40 KiB of shared memory
   int stretch = (40 * 1024 / 4) / (5 * heads);
   stretch = stretch < 1 ? 1 : (stretch > 256 ? 256 : stretch);
   FG_CHECK_ARG(5 * heads * 4 <= 40 * 1024, "fg_mlstm_scan: %d heads are too many", heads);
   mlstm_maxima_kernel<<<n_seqs, MX_THREADS, (size_t)stretch * 5 * heads * sizeof(float), stream>>>(
-      gates, coef, state, state_stride, m_offset, seq_slot, seq_start, heads, stretch);
+      gates, coef, state, state_stride, m_offset, seq_slot, seq_start, heads, stretch, few ? gate_bias : nullptr, cap);
   FG_CHECK_LAUNCH("fg_mlstm_scan (maxima)");
   if (dtype == FG_F32)
     return launch_scan((const float*)q, q_stride, (const float*)k, k_stride, (const float*)v, v_stride, coef, y,

@@ -1027,7 +1027,7 @@ class Ops:
             _ptr(gates), _ptr(gate_bias), float(cap), _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0),
             _code(q.dtype), _ptr(coef), _ptr(y), y.stride(0), _ptr(state), state.stride(0), _ptr(ctx.req),
             _ptr(ctx.seq_slot), _ptr(ctx.seq_start), t, ctx.n_seqs, heads, d, dv, float(q_scale), _stream()))
-        Ops.launches += 2  # the gates and the chain of running maxima
+        Ops.launches += 1 if t <= 4 * ctx.n_seqs else 2  # the chain of running maxima; the gates of many tokens
         return y, coef
 
     def mlstm_out(self, y, coef, z, weight, heads: int, dv: int, eps: float, ctx) -> torch.Tensor:

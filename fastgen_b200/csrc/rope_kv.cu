@@ -293,11 +293,60 @@ qk_head_factors_kernel(const T* q, long q_stride, const T* k, long k_stride, int
   if (lane == 0) out[(size_t)t * heads + h] = f;
 }
 
+// The same for bfloat16 rows that can be read in 16-byte pieces: eight lanes a (token, head), a piece of
+// eight columns a lane and round.
+__global__ void __launch_bounds__(128)
+qk_head_factors_bf16x8_kernel(const __nv_bfloat16* q, long q_stride, const __nv_bfloat16* k, long k_stride, int n_heads,
+                              int n_kv_heads, int head_dim, int real_dim, int norm, float eps, float temp_coef,
+                              int temp_every, const int* __restrict__ pos, const int* __restrict__ req,
+                              float* __restrict__ out, int n_tokens) {
+  const int heads = n_heads + n_kv_heads;
+  const long item = ((long)blockIdx.x * 128 + threadIdx.x) >> 3;
+  const int lane = threadIdx.x & 7;
+  const bool live = item < (long)n_tokens * heads;
+  const int t = live ? (int)(item / heads) : 0, h = live ? (int)(item % heads) : 0;
+  const bool active = live && req[t] >= 0;
+  float f = 1.f;
+  if (norm) {
+    float ss = 0.f;
+    if (active) {
+      const __nv_bfloat16* x = h < n_heads ? q + (size_t)t * q_stride + (size_t)h * head_dim
+                                           : k + (size_t)t * k_stride + (size_t)(h - n_heads) * head_dim;
+      for (int d = lane * 8; d < real_dim; d += 64) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(x + d);
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 v = __bfloat1622float2(h2[i]);
+          ss = fmaf(v.x, v.x, ss);
+          ss = fmaf(v.y, v.y, ss);
+        }
+      }
+    }
+    ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+    ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+    ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+    f = rsqrtf(ss / (float)real_dim + eps);
+  }
+  if (!active) return;
+  if (temp_every > 0 && h < n_heads) f *= 1.f + temp_coef * logf((float)((pos[t] + 1) / temp_every) + 1.f);
+  if (lane == 0) out[(size_t)t * heads + h] = f;
+}
+
 extern "C" int fg_qk_head_factors(const void* q, long q_stride, const void* k, long k_stride, int dtype, int n_heads,
                                   int n_kv_heads, int head_dim, int real_dim, int norm, float eps, float temp_coef,
                                   int temp_every, const int* pos, const int* req, float* out, int n_tokens,
                                   cudaStream_t stream) {
   if (n_tokens == 0) return 0;
+  if (dtype == FG_BF16 && head_dim % 8 == 0 && real_dim % 8 == 0 && q_stride % 8 == 0 && k_stride % 8 == 0 &&
+      ((uintptr_t)q & 15) == 0 && (k == nullptr || ((uintptr_t)k & 15) == 0)) {
+    const long lanes = (long)n_tokens * (n_heads + n_kv_heads) * 8;
+    qk_head_factors_bf16x8_kernel<<<(unsigned)((lanes + 127) / 128), 128, 0, stream>>>(
+        (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k, k_stride, n_heads, n_kv_heads, head_dim, real_dim, norm,
+        eps, temp_coef, temp_every, pos, req, out, n_tokens);
+    FG_CHECK_LAUNCH("fg_qk_head_factors");
+    return 0;
+  }
   FG_CHECK_ARG(n_heads > 0 && n_kv_heads >= 0 && real_dim > 0 && real_dim <= head_dim && (n_kv_heads == 0 || k || !norm),
                "fg_qk_head_factors: bad sizes");
   const long items = (long)n_tokens * (n_heads + n_kv_heads);

@@ -45,6 +45,8 @@ def test_every_declared_signature_belongs_to_its_library():
     latent = exported(["latent_mma.cu"])
     delta = exported(["delta_rule.cu"])
     moe = exported(["moe.cu"])
+    recur = exported(["mlstm.cu", "rglru.cu"])
+    assert set(ops._RECUR_SIGNATURES) <= recur, set(ops._RECUR_SIGNATURES) - recur
     assert set(ops._CORE_SIGNATURES) <= core, set(ops._CORE_SIGNATURES) - core
     assert set(ops._ATTN_SIGNATURES) <= attn, set(ops._ATTN_SIGNATURES) - attn
     assert set(ops._LATENT_SIGNATURES) <= latent, set(ops._LATENT_SIGNATURES) - latent
@@ -53,11 +55,11 @@ def test_every_declared_signature_belongs_to_its_library():
     # and every exported function that takes a pointer is declared
     called = set(re.findall(r"\blib\.(fg_\w+)\(", Path(ops.__file__).read_text()))
     undeclared = called - set(ops._CORE_SIGNATURES) - set(ops._ATTN_SIGNATURES) - set(ops._LATENT_SIGNATURES)
-    undeclared -= set(ops._DELTA_SIGNATURES) | set(ops._MOE_SIGNATURES)
+    undeclared -= set(ops._DELTA_SIGNATURES) | set(ops._MOE_SIGNATURES) | set(ops._RECUR_SIGNATURES)
     int_only = {"fg_attention_decode_scratch_floats", "fg_attention_decode_split", "fg_attention_prefill_rows",
                 "fg_attention_rows_per_block", "fg_last_error", "fg_attention_sigmoid_decode_keys",
                 "fg_latent_mma_rows", "fg_latent_mma_keys", "fg_latent_mma_scratch_floats",
-                "fg_moe_gemm_tile_rows", "fg_moe_mma_tile_rows"}
+                "fg_moe_gemm_tile_rows", "fg_moe_mma_tile_rows", "fg_mlstm_state_floats"}
     assert undeclared <= int_only, undeclared - int_only
 
 
