@@ -109,14 +109,28 @@ mlstm_maxima_kernel(const float* __restrict__ gates, float* __restrict__ coef, f
       }
       __syncthreads();
       if (h < heads) {
-        for (int tt = 0; tt < nt; ++tt) {
-          const float gi = g[tt * 2 * heads + h], gf = g[tt * 2 * heads + heads + h];
-          const float mn = fmaxf(gf + m, gi);
-          float* o = c + ((size_t)tt * heads + h) * 3;
-          o[0] = gf + m - mn;
-          o[1] = gi - mn;
-          o[2] = -mn;
-          m = mn;
+        // eight tokens' gates are read before their chain is walked: the chain is an addition and a
+        // maximum a token and must not wait for shared memory
+        constexpr int U = 8;
+        for (int t8 = 0; t8 < nt; t8 += U) {
+          float gi[U], gf[U];
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const int tt = min(t8 + u, nt - 1);
+            gi[u] = g[tt * 2 * heads + h];
+            gf[u] = g[tt * 2 * heads + heads + h];
+          }
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            if (t8 + u < nt) {
+              const float mn = fmaxf(gf[u] + m, gi[u]);
+              float* o = c + ((size_t)(t8 + u) * heads + h) * 3;
+              o[0] = gf[u] + m - mn;
+              o[1] = gi[u] - mn;
+              o[2] = -mn;
+              m = mn;
+            }
+          }
         }
       }
       __syncthreads();
@@ -245,6 +259,8 @@ mlstm_scan_kernel(const T* __restrict__ q, long q_stride, const T* __restrict__ 
   for (int stage = 0; stage < n_stages; ++stage) {
     const int ts = t0 + stage * MS_TOKENS, nt = min(MS_TOKENS, t1 - ts), buf = stage & 1;
     if (computes) {
+      // (unrolled: a token's sums over the lanes do not hold up the next token's update of S)
+#pragma unroll 4
       for (int tt = 0; tt < nt; ++tt) {
         const float kp = keep[buf][tt], vv = vs[buf][tt][cl];
         float acc0 = 0.f, acc1 = 0.f;
