@@ -113,7 +113,7 @@ def palulorn_config(width, layers, heads, kv, head_dim, ffn, vocab, window=1024,
     shared expert of that size.  All layers are one run that is passed once, so the pass opens by mixing
     the embedding output in and adding its step vector."""
     left = dict(heads=heads // 2, kv_heads=max(1, kv // 2), dim=head_dim, vdim=head_dim, scale=head_dim ** -0.5,
-                q_temp=dict(coef=0.1, every=256))
+                q_temp=dict(coef=0.1, every=512))
     right = dict(heads=heads // 2, dim=head_dim, vdim=head_dim, gate_cap=15.0)
     att = dict(heads=heads, kv_heads=kv, dim=head_dim, vdim=head_dim, scale=head_dim ** -0.5, conv=4,
                rot=dict(dims=head_dim // 2, base=500000.0, scaling=dict(factor=4.0)), mask=dict(size=window))
@@ -795,7 +795,7 @@ def palulorn_kernel_table(size, device, peaks) -> Dict[str, dict]:
         ctx = context(t, 1)
         logits = ops.moe_logits(x, router)
         route = lambda: ops.moe_route(logits, None, top, ctx, renormalize=True, score="sigmoid", groups=groups, renorm_eps=1e-20,
-                                      weight_scale=1.5)
+                                      weight_scale=2.0)
         ids, weights = route()
         row = dict(router_logits_us=round(timer.us(lambda: ops.moe_logits(x, router), graph=few(t)), 1),
                    choice_us=round(timer.us(route, graph=few(t)), 1))

@@ -329,7 +329,7 @@ PORTIONS = (33, 1, 1, 7, 1, 2, 3, 1, 26)
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("sizes", [(4, 2, 32, 0.15, (0.5, 7)), (1, 1, 64, 0.1, None), (5, 1, 16, 0.2, (0.3, 16)),
-                                   (2, 1, 32, 0.2, (1.0, 1)), (8, 1, 64, 0.125, (0.3, 40)), (2, 2, 128, 0.04, (0.6, 3)),
+                                   (2, 1, 32, 0.2, (1.0, 1)), (8, 2, 64, 0.11, (0.2, 40)), (2, 2, 128, 0.04, (0.6, 3)),
                                    (3, 3, 24, 0.3, None), (16, 2, 48, 0.14, (0.1, 50))])
 def test_attention_with_a_sink_alone(dtype, sizes):
     """Keys that are the values, biases, the temperature of the query's position, the sink in the
@@ -403,7 +403,7 @@ def test_far_key_beside_the_sink(dtype, mode, d):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("sizes", [(3, 24, 40, 10.0), (1, 33, 5, 4.0), (2, 160, 12, 15.0), (3, 16, 16, 8.0), (6, 48, 48, 15.0),
+@pytest.mark.parametrize("sizes", [(3, 24, 40, 10.0), (1, 33, 5, 4.0), (2, 160, 12, 15.0), (3, 16, 16, 8.0), (6, 40, 56, 12.0),
                                    (2, 64, 9, 2.0), (4, 128, 32, 15.0), (1, 256, 64, 5.0), (8, 32, 128, 30.0), (2, 8, 1, 1.0)])
 def test_matrix_memory_alone(dtype, sizes):
     """Capped log gates, the running maximum that starts at zero, state and normaliser, the floor of
@@ -487,7 +487,7 @@ def test_state_carries_what_was_long_ago(dtype, kind):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("sizes", [(80, 5, 3), (64, 1, 1), (120, 3, 4), (48, 2, 2), (320, 4, 4), (36, 36, 8), (256, 2, 5)])
+@pytest.mark.parametrize("sizes", [(80, 5, 3), (64, 1, 1), (120, 3, 4), (48, 2, 2), (288, 4, 3), (36, 36, 8), (256, 2, 5)])
 def test_gated_linear_recurrence_alone(dtype, sizes):
     """Both branches, the convolution with its bias and its last inputs, the block-diagonal gate maps,
     the decay and the recurrence from zero: a prompt portion, single tokens and short portions through
@@ -517,7 +517,7 @@ def test_gated_linear_recurrence_alone(dtype, sizes):
     (2, 2, 64, 64, 0.12, 3, (64, 1e4, 2.0), 70),
     (2, 2, 80, 16, 0.11, 2, (40, 2000.0, 4.0), 1),
     (3, 1, 16, 16, 0.25, 8, (8, 100.0, None), 33),
-    (4, 2, 96, 64, 0.08, 3, (96, 1e6, 4.0), 24),
+    (4, 2, 96, 48, 0.08, 2, (48, 1e5, 3.0), 24),
     (2, 1, 128, 128, 0.09, 2, (64, 1e4, 2.0), None),
 ])
 def test_window_attention_alone(dtype, sizes):
@@ -629,7 +629,7 @@ def _clear_choices(x, mlp, w, margin):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("sizes", [(6, 3, 40, (3, 2), 2.0, 24), (5, 2, 24, None, 1.0, None), (8, 1, 16, (4, 1), 0.5, 8),
                                    (1, 1, 56, None, 1.0, None), (4, 4, 16, (2, 2), 1.0, 16), (9, 4, 8, (3, 2), 2.5, None),
-                                   (8, 2, 96, (4, 3), 1.5, 96), (64, 6, 24, (8, 3), 1.0, 8), (33, 5, 16, (33, 7), 3.0, None),
+                                   (8, 3, 80, (4, 3), 1.25, 48), (64, 6, 24, (8, 3), 1.0, 8), (33, 5, 16, (33, 7), 3.0, None),
                                    (12, 2, 32, (2, 1), 1.0, 16)])
 @pytest.mark.parametrize("tokens", [1, 3, 70, 600])
 def test_routed_experts_alone(dtype, sizes, tokens):
@@ -773,7 +773,7 @@ def test_batching_changes_nothing(tmp_path, dtype, name):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
-@pytest.mark.parametrize("name", ["pa", "pc"])
+@pytest.mark.parametrize("name", ["pa", "pb", "pc"])
 def test_steps_replayed_from_graphs_change_nothing(tmp_path, dtype, name):
     """Steps captured as CUDA graphs (single tokens, and prompt portions padded to a few shapes) give
     what the same steps give launched kernel by kernel: states and convolution inputs are advanced by the
