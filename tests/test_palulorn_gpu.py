@@ -113,7 +113,20 @@ PD = dict(
         _layer("attention", _attn(3, 1, 16, 16, 0.25, conv=8, rot=(8, 100.0, None), window=33), _moe(2, 1, 24)),
     ],
 )
-CONFIGS = {"pa": (PA, 3), "pb": (PB, 5), "pc": (PC, 8), "pd": (PD, 9)}
+# sizes that fit no kernel's favourite: a width that is no multiple of eight, heads in groups of three,
+# head sizes that are padded, a memory of 200 rows, a window longer than any prompt here, a run of two
+# layers in the middle passed four times, sixteen experts in eight groups
+PE = dict(
+    architecture="Palulorn", vocab=173, width=100, norm=dict(eps=1e-6), embedding=dict(scale=7.5),
+    loop=dict(start=1, stop=3, times=4),
+    layers=[
+        _layer("attention", _attn(6, 2, 40, 24, 0.16, conv=1, rot=(20, 777.0, 2.5), window=500), _moe(16, 4, 12, (8, 3), 1.75, 20)),
+        _layer("rglru", _lru(72, 3, 5), _moe(3, 2, 28)),
+        _layer("parallel", _pair(_sink(6, 2, 80, 0.1, (0.7, 5)), _memory(1, 200, 36, 20.0)), None),
+        _layer("parallel", _pair(_sink(3, 3, 16, 0.3), _memory(5, 8, 24, 3.0)), _moe(2, 2, 36, (1, 1), 0.8, 4)),
+    ],
+)
+CONFIGS = {"pa": (PA, 3), "pb": (PB, 5), "pc": (PC, 8), "pd": (PD, 9), "pe": (PE, 12)}
 
 
 def make_dir(tmp_path, name, std=0.1):
@@ -728,7 +741,7 @@ def model_dir(tmp_path, name, dtype):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
-@pytest.mark.parametrize("name", ["pa", "pb", "pc", "pd"])
+@pytest.mark.parametrize("name", ["pa", "pb", "pc", "pd", "pe"])
 @pytest.mark.parametrize("plan", ["whole", "decode", "portions", "mixed"])
 def test_replay(tmp_path, name, dtype, plan):
     """Whole prompts (of one and two tokens too), prompts with a decoded tail that passes the windows,
